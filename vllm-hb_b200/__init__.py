@@ -1,0 +1,674 @@
+"""ctypes binding of libhb.so — the B200 tensor-parallel decode hot path of vllm-hb.
+
+The product is the C ABI declared in ``include/hb.h``; this module is the thin host
+mirror that the tests and ``bench.py`` use.  Names follow the reference's modules:
+
+    kernels.rms_norm.apply / kernels.rope.apply / kernels.kv_assign.assign_slot
+        (src/kernels/{rms_norm,rope,kv_assign}.rs)
+    parallel.TpWorld, parallel.column_shard / row_shard
+        (src/parallel/{world,shard}.rs)
+    scheduler.BlockManager (src/scheduler/block_manager.rs)
+    Engine (src/engine/loader.rs)
+
+There is no CPU fallback: a missing library raises at import, a missing GPU makes the
+compute calls fail with ``HbError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libhb.so"
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python vllm-hb_b200/build.py` "
+        "(there is no fallback path)"
+    )
+
+lib = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+
+F32, F16, BF16 = 0, 1, 2
+ALGO_AUTO, ALGO_ONE_SHOT, ALGO_TWO_SHOT, ALGO_NCCL = 0, 1, 2, 3
+BLOCK_SIZE = 16
+IPC_HANDLE_BYTES = 64
+NCCL_ID_BYTES = 128
+MAX_RANKS = 8
+
+ERR_INVALID_ARG, ERR_UNSUPPORTED_DTYPE, ERR_NOT_DIVISIBLE, ERR_CUDA = -1, -2, -3, -4
+ERR_NCCL, ERR_TIMEOUT, ERR_OOM_BLOCKS, ERR_IO, ERR_EMPTY = -5, -6, -7, -8, -9
+
+
+class HbError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+        self.msg = msg
+
+
+class ModelConfig(C.Structure):
+    """hb_model_config: ModelConfig of src/engine/config.rs:14-26 plus rank-side additions."""
+    _fields_ = [
+        ("model_path", C.c_char_p),
+        ("max_seq_len", C.c_size_t),
+        ("gpu_memory_utilization", C.c_double),
+        ("bf16", C.c_int),
+        ("tensor_parallel_size", C.c_int),
+        ("num_kv_blocks", C.c_int64),
+        ("max_batch", C.c_int),
+        ("force_f32", C.c_int),
+    ]
+
+
+class ModelShape(C.Structure):
+    _fields_ = [
+        ("hidden_size", C.c_int64),
+        ("intermediate_size", C.c_int64),
+        ("num_hidden_layers", C.c_int64),
+        ("num_attention_heads", C.c_int64),
+        ("num_key_value_heads", C.c_int64),
+        ("vocab_size", C.c_int64),
+        ("rms_norm_eps", C.c_double),
+        ("rope_theta", C.c_double),
+    ]
+
+
+_vp, _i, _i64, _f, _sz, _u64 = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t, C.c_uint64
+
+_SIGS = {
+    "hb_last_error": (C.c_char_p, []),
+    "hb_version": (C.c_char_p, []),
+    "hb_device_count": (_i, []),
+    "hb_rms_norm": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _i]),
+    "hb_add_rms_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i]),
+    "hb_rope_inv_freq": (_i, [_f, _i, _vp]),
+    "hb_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i]),
+    "hb_rope_cos_sin": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i]),
+    "hb_kv_assign_contig": (_i, [_vp, _vp, _vp, _i, _i64, _i, _i64, _i]),
+    "hb_kv_assign_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i]),
+    "hb_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
+    "hb_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _vp, _i]),
+    "hb_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
+    "hb_gemm": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
+    "hb_silu_mul": (_i, [_vp, _vp, _vp, _i64, _i64, _i]),
+    "hb_embed": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
+    "hb_argmax": (_i, [_vp, _vp, _vp, _i64, _i64, _i]),
+    "hb_world_create_local": (_i, [_i, _vp, _sz, _vp]),
+    "hb_world_create_rank": (_i, [_i, _i, _i, _sz, _vp]),
+    "hb_world_ipc_handle": (_i, [_vp, _vp]),
+    "hb_world_attach": (_i, [_vp, _vp]),
+    "hb_world_attach_ptrs": (_i, [_vp, _vp]),
+    "hb_nccl_unique_id": (_i, [_vp]),
+    "hb_world_init_nccl": (_i, [_vp, _vp]),
+    "hb_world_free": (_i, [_vp]),
+    "hb_world_size": (_i, [_vp]),
+    "hb_world_rank": (_i, [_vp]),
+    "hb_world_device": (_i, [_vp]),
+    "hb_world_is_single": (_i, [_vp]),
+    "hb_world_staging_bytes": (_sz, [_vp]),
+    "hb_world_stream": (_vp, [_vp]),
+    "hb_world_status": (_i, [_vp]),
+    "hb_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i]),
+    "hb_fused_rowparallel_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "hb_fused_rowparallel": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f, _i, _vp]),
+    "hb_column_shard": (_i, [_vp, _vp, _i64, _i64, _sz, _i, _i]),
+    "hb_row_shard": (_i, [_vp, _vp, _i64, _i64, _sz, _i, _i]),
+    "hb_bm_create": (_i, [_i64, _i64, _vp]),
+    "hb_bm_free_manager": (_i, [_vp]),
+    "hb_bm_num_free_gpu_blocks": (_i64, [_vp]),
+    "hb_bm_num_free_cpu_blocks": (_i64, [_vp]),
+    "hb_bm_num_prefix_cached_blocks": (_i64, [_vp]),
+    "hb_bm_allocate": (_i, [_vp, _u64, _vp, _i64, _i64, _vp]),
+    "hb_bm_can_allocate": (_i, [_vp, _i64]),
+    "hb_bm_can_append_slot": (_i, [_vp, _u64, _i64]),
+    "hb_bm_append_slot": (_i, [_vp, _u64, _i64, _vp]),
+    "hb_bm_free_seq": (_i, [_vp, _u64]),
+    "hb_bm_swap_out": (_i, [_vp, _u64, _vp, _vp]),
+    "hb_bm_swap_in": (_i, [_vp, _u64, _vp, _vp]),
+    "hb_bm_block_table": (_i64, [_vp, _u64, _vp, _i64]),
+    "hb_hash_block": (_u64, [_vp, _i64]),
+    "hb_num_logical_blocks": (_i64, [_i64, _i64]),
+    "hb_last_block_num_filled": (_i64, [_i64, _i64]),
+    "hb_slot_for_position": (_i64, [_vp, _i64, _i64]),
+    "hb_engine_load": (_i, [_vp, _vp, _vp]),
+    "hb_engine_create_random": (_i, [_vp, _vp, _vp, _u64, _f, _i, _vp]),
+    "hb_engine_free": (_i, [_vp]),
+    "hb_engine_num_layers": (_i64, [_vp]),
+    "hb_engine_vocab_size": (_i64, [_vp]),
+    "hb_engine_hidden_size": (_i64, [_vp]),
+    "hb_engine_param_count": (_i64, [_vp]),
+    "hb_engine_num_free_blocks": (_i64, [_vp]),
+    "hb_engine_step_bytes": (C.c_double, [_vp, _vp, _i64]),
+    "hb_engine_get_tensor": (_i64, [_vp, C.c_char_p, _vp, _i64]),
+    "hb_seq_create": (_i, [_vp, _vp]),
+    "hb_seq_free": (_i, [_vp, _vp]),
+    "hb_seq_len": (_i64, [_vp]),
+    "hb_seq_block_table": (_i64, [_vp, _vp, _i64]),
+    "hb_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
+    "hb_decode_batch": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "hb_engine_last_step_ms": (_f, [_vp]),
+    "hb_engine_last_step_launches": (_i64, [_vp]),
+    "hb_engine_stream": (_vp, [_vp]),
+}
+
+#: every symbol include/hb.h declares (tests check the library exports all of them)
+DECLARED_SYMBOLS = tuple(_SIGS)
+
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.hb_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int) -> int:
+    if rc < 0:
+        raise HbError(rc, last_error())
+    return rc
+
+
+def device_count() -> int:
+    return lib.hb_device_count()
+
+
+# --------------------------------------------------------------------------- dtypes
+def dtype_code(t) -> int:
+    """Map a torch or numpy dtype to hb_dtype."""
+    name = str(t).replace("torch.", "")
+    try:
+        return {"float32": F32, "float16": F16, "bfloat16": BF16}[name]
+    except KeyError:
+        raise HbError(ERR_UNSUPPORTED_DTYPE, f"unsupported dtype {t}") from None
+
+
+def _ptr(x) -> Optional[int]:
+    """Raw address of a torch tensor / numpy array / int / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    return x.data_ptr()
+
+
+def _stream(stream=None) -> Optional[int]:
+    if stream is None:
+        try:
+            import torch
+
+            if torch.cuda.is_available():
+                return torch.cuda.current_stream().cuda_stream
+        except Exception:
+            pass
+        return None
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+# ------------------------------------------------------------------ kernels mirror
+class kernels:
+    """Mirror of src/kernels: caller-allocated outputs, torch CUDA tensors in."""
+
+    class rms_norm:
+        @staticmethod
+        def apply(x, weight, eps: float, out=None, stream=None):
+            """rms_norm::apply (src/kernels/rms_norm.rs:23)."""
+            import torch
+
+            hidden = x.shape[-1]
+            rows = x.numel() // hidden if hidden else 0
+            out = torch.empty_like(x) if out is None else out
+            check(lib.hb_rms_norm(_stream(stream), _ptr(out), _ptr(x), _ptr(weight), rows, hidden,
+                                  float(eps), dtype_code(x.dtype)))
+            return out
+
+        @staticmethod
+        def add_apply(x, resid, weight, eps: float, stream=None):
+            """Residual add + norm; returns (normed, new_residual)."""
+            import torch
+
+            hidden = x.shape[-1]
+            rows = x.numel() // hidden
+            normed, res = torch.empty_like(x), torch.empty_like(x)
+            check(lib.hb_add_rms_norm(_stream(stream), _ptr(normed), _ptr(res), _ptr(x), _ptr(resid),
+                                      _ptr(weight), rows, hidden, float(eps), dtype_code(x.dtype)))
+            return normed, res
+
+    class rope:
+        @staticmethod
+        def inv_freq(theta: float, head_dim: int) -> np.ndarray:
+            out = np.empty(head_dim // 2, dtype=np.float32)
+            check(lib.hb_rope_inv_freq(float(theta), head_dim, out.ctypes.data))
+            return out
+
+        @staticmethod
+        def apply(q, k, cos, sin, stream=None):
+            """rope::apply (src/kernels/rope.rs:25): q,k [b,h,s,d], cos/sin [s,d/2]."""
+            import torch
+
+            outs = []
+            for x in (q, k):
+                b, h, s, d = x.shape
+                o = torch.empty_like(x)
+                check(lib.hb_rope_cos_sin(_stream(stream), _ptr(o), _ptr(x), _ptr(cos), _ptr(sin),
+                                          b * h, s, d, dtype_code(x.dtype)))
+                outs.append(o)
+            return outs[0], outs[1]
+
+        @staticmethod
+        def apply_positions(q, k, positions, inv_freq, stream=None):
+            """In place on q [t,hq,d] and k [t,hkv,d] with per-token positions."""
+            t, hq, d = q.shape
+            hkv = k.shape[1] if k is not None else 0
+            check(lib.hb_rope(_stream(stream), _ptr(q), _ptr(k), _ptr(positions), _ptr(inv_freq), t,
+                              hq, hkv, d, dtype_code(q.dtype)))
+            return q, k
+
+    class kv_assign:
+        @staticmethod
+        def assign_slot(buf, src, offset: int, stream=None):
+            """kv_assign::assign_slot (src/kernels/kv_assign.rs:34): buf [1,nkv,max_seq,d],
+            src [1,nkv,1,d]; written in place and returned."""
+            _, nkv, max_seq, d = buf.shape
+            check(lib.hb_kv_assign_contig(_stream(stream), _ptr(buf), _ptr(src), nkv, max_seq, d,
+                                          int(offset), dtype_code(buf.dtype)))
+            return buf
+
+        @staticmethod
+        def assign_paged(k_cache, v_cache, k, v, slot_mapping, stream=None):
+            num_blocks, nkv, _, d = k_cache.shape
+            check(lib.hb_kv_assign_paged(_stream(stream), _ptr(k_cache), _ptr(v_cache), _ptr(k), _ptr(v),
+                                         _ptr(slot_mapping), k.shape[0], nkv, d, num_blocks,
+                                         dtype_code(k.dtype)))
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, n_splits: int = 1, stream=None):
+    """q [n_seqs,hq,d]; caches [num_blocks,hkv,16,d]; block_tables int32 [n_seqs,max_blocks]."""
+    import torch
+
+    n_seqs, hq, d = q.shape
+    num_blocks, hkv = k_cache.shape[0], k_cache.shape[1]
+    out = torch.empty_like(q)
+    ws_bytes = lib.hb_attention_workspace_bytes(n_seqs, hq, d, n_splits)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+    check(lib.hb_paged_decode_attention(_stream(stream), _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                        _ptr(block_tables), _ptr(ctx_lens), n_seqs, hq, hkv, d,
+                                        block_tables.shape[1], num_blocks, n_splits, _ptr(ws),
+                                        dtype_code(q.dtype)))
+    return out
+
+
+def gemm(x, w, stream=None):
+    """y = x @ w.T with w stored [out, in]."""
+    import torch
+
+    M, K = x.shape
+    N = w.shape[0]
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    code = dtype_code(x.dtype)
+    ws_bytes = lib.hb_gemm_workspace_bytes(M, N, K, code)
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    check(lib.hb_gemm(_stream(stream), _ptr(y), _ptr(x), _ptr(w), M, N, K, code, _ptr(ws)))
+    return y
+
+
+def silu_mul(gate_up, stream=None):
+    import torch
+
+    M, two_i = gate_up.shape
+    out = torch.empty((M, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(lib.hb_silu_mul(_stream(stream), _ptr(out), _ptr(gate_up), M, two_i // 2, dtype_code(gate_up.dtype)))
+    return out
+
+
+def embed(table, ids, stream=None):
+    import torch
+
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    check(lib.hb_embed(_stream(stream), _ptr(out), _ptr(table), _ptr(ids), ids.numel(), table.shape[1],
+                       table.shape[0], dtype_code(table.dtype)))
+    return out
+
+
+def argmax(logits, stream=None):
+    import torch
+
+    n, vocab = logits.shape
+    out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    check(lib.hb_argmax(_stream(stream), _ptr(out), _ptr(logits), n, vocab, dtype_code(logits.dtype)))
+    return out
+
+
+# ----------------------------------------------------------------- parallel mirror
+def column_shard(weight: np.ndarray, rank: int, world_size: int) -> np.ndarray:
+    """column_shard (src/parallel/shard.rs:46)."""
+    w = np.ascontiguousarray(weight)
+    rows, cols = w.shape
+    out = np.empty((rows // max(world_size, 1), cols), dtype=w.dtype)
+    check(lib.hb_column_shard(out.ctypes.data, w.ctypes.data, rows, cols, w.itemsize, rank, world_size))
+    return out
+
+
+def row_shard(weight: np.ndarray, rank: int, world_size: int) -> np.ndarray:
+    """row_shard (src/parallel/shard.rs:66)."""
+    w = np.ascontiguousarray(weight)
+    rows, cols = w.shape
+    out = np.empty((rows, cols // max(world_size, 1)), dtype=w.dtype)
+    check(lib.hb_row_shard(out.ctypes.data, w.ctypes.data, rows, cols, w.itemsize, rank, world_size))
+    return out
+
+
+class TpWorld:
+    """One rank's side of a tensor-parallel group (TpWorld, src/parallel/world.rs)."""
+
+    def __init__(self, handle: int, owner: bool = True):
+        self.handle = handle
+        self._owner = owner
+
+    # --- constructors
+    @classmethod
+    def new_local(cls, n: int, device_ids: Optional[Sequence[int]] = None,
+                  staging_bytes: int = 64 << 20) -> list["TpWorld"]:
+        """Single-process form of TpWorld::new(n): one handle per rank."""
+        arr = (C.c_void_p * n)()
+        ids = (C.c_int * n)(*device_ids) if device_ids is not None else None
+        check(lib.hb_world_create_local(n, ids, staging_bytes, arr))
+        return [cls(arr[i]) for i in range(n)]
+
+    @classmethod
+    def new_rank(cls, world_size: int, rank: int, device: int, staging_bytes: int = 64 << 20) -> "TpWorld":
+        h = C.c_void_p()
+        check(lib.hb_world_create_rank(world_size, rank, device, staging_bytes, C.byref(h)))
+        return cls(h.value)
+
+    @classmethod
+    def from_torch_distributed(cls, device: int, staging_bytes: int = 64 << 20, nccl: bool = False) -> "TpWorld":
+        """One process per GPU: exchange the IPC handles over torch.distributed."""
+        import torch.distributed as dist
+
+        ws, rank = dist.get_world_size(), dist.get_rank()
+        w = cls.new_rank(ws, rank, device, staging_bytes)
+        if ws > 1:
+            handles: list = [None] * ws
+            dist.all_gather_object(handles, w.ipc_handle())
+            w.attach(b"".join(handles))
+            if nccl:
+                box = [w.nccl_unique_id() if rank == 0 else None]
+                dist.broadcast_object_list(box, src=0)
+                w.init_nccl(box[0])
+            dist.barrier()
+        return w
+
+    # --- plumbing
+    def ipc_handle(self) -> bytes:
+        buf = C.create_string_buffer(IPC_HANDLE_BYTES)
+        check(lib.hb_world_ipc_handle(self.handle, buf))
+        return buf.raw
+
+    def attach(self, all_handles: bytes) -> None:
+        check(lib.hb_world_attach(self.handle, all_handles))
+
+    @staticmethod
+    def nccl_unique_id() -> bytes:
+        buf = C.create_string_buffer(NCCL_ID_BYTES)
+        check(lib.hb_nccl_unique_id(buf))
+        return buf.raw
+
+    def init_nccl(self, uid: bytes) -> None:
+        check(lib.hb_world_init_nccl(self.handle, uid))
+
+    # --- TpWorld surface
+    def world_size(self) -> int:
+        return lib.hb_world_size(self.handle)
+
+    def rank(self) -> int:
+        return lib.hb_world_rank(self.handle)
+
+    def device(self) -> int:
+        return lib.hb_world_device(self.handle)
+
+    def is_single(self) -> bool:
+        return bool(lib.hb_world_is_single(self.handle))
+
+    def status(self) -> int:
+        return lib.hb_world_status(self.handle)
+
+    def all_reduce(self, buf, algo: int = ALGO_AUTO, stream=None):
+        """In-place SUM over ranks of a torch CUDA tensor (TpWorld::all_reduce)."""
+        check(lib.hb_all_reduce(self.handle, _stream(stream), _ptr(buf), buf.numel(),
+                                dtype_code(buf.dtype), algo))
+        return buf
+
+    def fused_rowparallel(self, x, w, resid, norm_w, eps: float, algo: int = ALGO_AUTO, stream=None):
+        """(normed, new_resid) = fused o_proj/down_proj + all-reduce + residual + RMSNorm."""
+        import torch
+
+        M, Kl = x.shape
+        N = w.shape[0]
+        normed = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        res = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        ws_bytes = lib.hb_fused_rowparallel_workspace_bytes(M, N, Kl)
+        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+        check(lib.hb_fused_rowparallel(self.handle, _stream(stream), _ptr(normed), _ptr(res), _ptr(x), _ptr(w),
+                                       _ptr(resid), _ptr(norm_w), M, N, Kl, float(eps), algo, _ptr(ws)))
+        return normed, res
+
+    def close(self) -> None:
+        if self.handle and self._owner:
+            lib.hb_world_free(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------- scheduler mirror
+class BlockManager:
+    """BlockManager (src/scheduler/block_manager.rs:143-414), one sequence per group."""
+
+    def __init__(self, num_gpu_blocks: int, num_cpu_blocks: int):
+        h = C.c_void_p()
+        check(lib.hb_bm_create(num_gpu_blocks, num_cpu_blocks, C.byref(h)))
+        self.handle = h.value
+
+    def num_free_gpu_blocks(self) -> int:
+        return lib.hb_bm_num_free_gpu_blocks(self.handle)
+
+    def num_free_cpu_blocks(self) -> int:
+        return lib.hb_bm_num_free_cpu_blocks(self.handle)
+
+    def num_prefix_cached_blocks(self) -> int:
+        return lib.hb_bm_num_prefix_cached_blocks(self.handle)
+
+    def can_allocate(self, total_len: int) -> bool:
+        return bool(lib.hb_bm_can_allocate(self.handle, total_len))
+
+    def allocate(self, seq_id: int, prompt_ids: Sequence[int], output_len: int = 0) -> int:
+        ids = np.ascontiguousarray(np.asarray(prompt_ids, dtype=np.uint32))
+        hits = C.c_int64(0)
+        check(lib.hb_bm_allocate(self.handle, seq_id, ids.ctypes.data, len(ids), output_len, C.byref(hits)))
+        return hits.value
+
+    def free(self, seq_id: int) -> None:
+        check(lib.hb_bm_free_seq(self.handle, seq_id))
+
+    def can_append_slot(self, seq_id: int, total_len: int) -> bool:
+        return bool(lib.hb_bm_can_append_slot(self.handle, seq_id, total_len))
+
+    def append_slot(self, seq_id: int, total_len: int) -> list[tuple[int, int]]:
+        pair = (C.c_int64 * 2)()
+        check(lib.hb_bm_append_slot(self.handle, seq_id, total_len, pair))
+        return [] if pair[0] < 0 else [(pair[0], pair[1])]
+
+    def _swap(self, fn, seq_id: int) -> list[tuple[int, int]]:
+        n_tab = max(lib.hb_bm_block_table(self.handle, seq_id, None, 0), 0)
+        buf = (C.c_int64 * (2 * max(n_tab, 1)))()
+        n = C.c_int64(0)
+        check(fn(self.handle, seq_id, buf, C.byref(n)))
+        return [(buf[2 * i], buf[2 * i + 1]) for i in range(n.value)]
+
+    def swap_out(self, seq_id: int) -> list[tuple[int, int]]:
+        return self._swap(lib.hb_bm_swap_out, seq_id)
+
+    def swap_in(self, seq_id: int) -> list[tuple[int, int]]:
+        return self._swap(lib.hb_bm_swap_in, seq_id)
+
+    def get_block_table(self, seq_id: int) -> Optional[list[int]]:
+        n = lib.hb_bm_block_table(self.handle, seq_id, None, 0)
+        if n < 0:
+            return None
+        buf = (C.c_int64 * max(n, 1))()
+        lib.hb_bm_block_table(self.handle, seq_id, buf, n)
+        return [buf[i] for i in range(n)]
+
+    def close(self) -> None:
+        if self.handle:
+            lib.hb_bm_free_manager(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def hash_block(tokens: Sequence[int]) -> int:
+    ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.uint32))
+    return lib.hb_hash_block(ids.ctypes.data, len(ids))
+
+
+# ------------------------------------------------------------------- engine mirror
+class Sequence_:
+    def __init__(self, engine: "Engine", handle: int):
+        self.engine, self.handle = engine, handle
+
+    def __len__(self) -> int:
+        return lib.hb_seq_len(self.handle)
+
+    def block_table(self) -> list[int]:
+        n = lib.hb_seq_block_table(self.handle, None, 0)
+        buf = (C.c_int64 * max(n, 1))()
+        lib.hb_seq_block_table(self.handle, buf, n)
+        return [buf[i] for i in range(n)]
+
+    def free(self) -> None:
+        if self.handle and self.engine.handle:
+            lib.hb_seq_free(self.engine.handle, self.handle)
+        self.handle = None
+
+
+class Engine:
+    """Engine (src/engine/loader.rs:66-339) for the TP Llama path."""
+
+    def __init__(self, handle: int, world: Optional[TpWorld]):
+        self.handle = handle
+        self.world = world
+
+    @staticmethod
+    def _config(model_path: Optional[str], max_seq_len: int, bf16: bool, tp: int, num_kv_blocks: int,
+                max_batch: int, force_f32: bool) -> ModelConfig:
+        return ModelConfig(model_path.encode() if model_path else None, max_seq_len, 0.9, int(bf16), tp,
+                           num_kv_blocks, max_batch, int(force_f32))
+
+    @classmethod
+    def load(cls, model_path: str, *, max_seq_len: int = 2048, bf16: bool = True,
+             tensor_parallel_size: int = 1, world: Optional[TpWorld] = None, num_kv_blocks: int = 0,
+             max_batch: int = 64, force_f32: bool = False) -> "Engine":
+        cfg = cls._config(model_path, max_seq_len, bf16, tensor_parallel_size, num_kv_blocks, max_batch,
+                          force_f32)
+        h = C.c_void_p()
+        check(lib.hb_engine_load(C.byref(cfg), world.handle if world else None, C.byref(h)))
+        return cls(h.value, world)
+
+    @classmethod
+    def create_random(cls, shape: dict, *, seed: int = 1, std: float = 0.02, norm_ones: bool = True,
+                      max_seq_len: int = 2048, bf16: bool = True, tensor_parallel_size: int = 1,
+                      world: Optional[TpWorld] = None, num_kv_blocks: int = 0, max_batch: int = 64,
+                      force_f32: bool = False) -> "Engine":
+        cfg = cls._config(None, max_seq_len, bf16, tensor_parallel_size, num_kv_blocks, max_batch, force_f32)
+        sh = ModelShape(shape["hidden_size"], shape["intermediate_size"], shape["num_hidden_layers"],
+                        shape["num_attention_heads"], shape.get("num_key_value_heads", 0),
+                        shape["vocab_size"], shape.get("rms_norm_eps", 1e-5), shape.get("rope_theta", 10000.0))
+        h = C.c_void_p()
+        check(lib.hb_engine_create_random(C.byref(sh), C.byref(cfg), world.handle if world else None,
+                                          seed, std, int(norm_ones), C.byref(h)))
+        return cls(h.value, world)
+
+    def num_layers(self) -> int:
+        return lib.hb_engine_num_layers(self.handle)
+
+    def vocab_size(self) -> int:
+        return lib.hb_engine_vocab_size(self.handle)
+
+    def hidden_size(self) -> int:
+        return lib.hb_engine_hidden_size(self.handle)
+
+    def param_count(self) -> int:
+        return lib.hb_engine_param_count(self.handle)
+
+    def num_free_blocks(self) -> int:
+        return lib.hb_engine_num_free_blocks(self.handle)
+
+    def step_bytes(self, ctx_lens: Sequence[int]) -> float:
+        a = np.ascontiguousarray(np.asarray(ctx_lens, dtype=np.int32))
+        return lib.hb_engine_step_bytes(self.handle, a.ctypes.data, len(a))
+
+    def get_tensor(self, name: str) -> np.ndarray:
+        n = check(lib.hb_engine_get_tensor(self.handle, name.encode(), None, 0))
+        out = np.empty(n, dtype=np.float32)
+        check(lib.hb_engine_get_tensor(self.handle, name.encode(), out.ctypes.data, n))
+        return out
+
+    def create_kv_cache(self) -> Sequence_:
+        h = C.c_void_p()
+        check(lib.hb_seq_create(self.handle, C.byref(h)))
+        return Sequence_(self, h.value)
+
+    def forward_with_cache(self, token_ids: Sequence[int], seq_pos: int, cache: Sequence_) -> np.ndarray:
+        """Last-token logits [vocab] as float32 (Engine::forward_with_cache)."""
+        ids = np.ascontiguousarray(np.asarray(token_ids, dtype=np.uint32))
+        logits = np.empty(self.vocab_size(), dtype=np.float32)
+        check(lib.hb_forward(self.handle, cache.handle, ids.ctypes.data, len(ids), seq_pos, logits.ctypes.data))
+        return logits
+
+    def decode_batch(self, seqs: Sequence[Sequence_], last_tokens: np.ndarray,
+                     next_tokens: Optional[np.ndarray] = None, logits: Optional[np.ndarray] = None) -> np.ndarray:
+        B = len(seqs)
+        arr = (C.c_void_p * B)(*[s.handle for s in seqs])
+        last = np.ascontiguousarray(np.asarray(last_tokens, dtype=np.uint32))
+        if next_tokens is None:
+            next_tokens = np.empty(B, dtype=np.uint32)
+        check(lib.hb_decode_batch(self.handle, arr, B, last.ctypes.data, next_tokens.ctypes.data,
+                                  logits.ctypes.data if logits is not None else None))
+        return next_tokens
+
+    def last_step_ms(self) -> float:
+        return lib.hb_engine_last_step_ms(self.handle)
+
+    def last_step_launches(self) -> int:
+        return lib.hb_engine_last_step_launches(self.handle)
+
+    def close(self) -> None:
+        if self.handle:
+            lib.hb_engine_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

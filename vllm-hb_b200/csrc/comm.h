@@ -1,0 +1,51 @@
+// Internal view of a tensor-parallel world (one rank's side).
+#pragma once
+
+#include "common.h"
+
+// Layout of every rank's staging buffer (all ranks use the same offsets, so a peer's
+// flag or data slot is peer_base + the same offset):
+//   [0, kFlagBytes)         flags and counters
+//   [kFlagBytes, size)      data area (partials pushed by peers, reduced slices)
+namespace hb {
+
+constexpr int kMaxCommCtas = 128;
+constexpr size_t kFlagBytes = 64 * 1024;
+
+struct CommFlags {
+  // written by peers (release, system scope), polled locally
+  uint32_t done[HB_MAX_RANKS];                      // calls completed by rank p
+  uint32_t arrive1[kMaxCommCtas][HB_MAX_RANKS];     // per-CTA: partials pushed
+  uint32_t arrive2[kMaxCommCtas][HB_MAX_RANKS];     // per-CTA: reduced slice pushed
+  uint32_t tile_arrive[2048];                       // fused kernel: partial tiles received per owned tile
+  uint32_t gather_arrive[HB_MAX_RANKS];             // fused kernel: reduced tiles received from rank p
+  // local only
+  uint32_t seq;        // collectives completed on this rank
+  uint32_t finished;   // CTAs of the running kernel that are done
+  int32_t status;      // 0 or HB_ERR_TIMEOUT
+  uint32_t local_tiles_done;  // fused kernel, single-rank barrier
+};
+static_assert(sizeof(CommFlags) <= kFlagBytes, "flag block too large");
+
+}  // namespace hb
+
+struct hb_world {
+  int ws = 1, rank = 0, device = 0;
+  cudaStream_t stream = nullptr;
+  size_t staging_bytes = 0;
+  void* local = nullptr;              // this rank's staging (cudaMalloc)
+  void* peer[HB_MAX_RANKS] = {};      // peer[rank] == local
+  bool ipc_open[HB_MAX_RANKS] = {};   // peer[p] came from cudaIpcOpenMemHandle
+  bool owns_local = true;
+  bool attached = false;
+  void* nccl = nullptr;               // ncclComm_t when hb_world_init_nccl ran
+  int32_t* host_status = nullptr;     // pinned mirror for hb_world_status
+};
+
+namespace hb {
+
+// In-place all-reduce on `st`; the building block of hb_all_reduce and of the engine.
+int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_dtype dtype,
+                     hb_algo algo);
+
+}  // namespace hb

@@ -1,0 +1,163 @@
+// Engine-internal kernels: fused RoPE + paged KV write on the [q|k|v] projection row,
+// device-side weight initialisation, dtype conversion.
+#include "common.h"
+#include "ops.h"
+
+namespace hb {
+
+constexpr int kRkThreads = 128;
+
+// One CTA per token.  Row layout: [q (nq*hd) | k (nkv*hd) | v (nkv*hd)].
+// q is rotated in place; rotated k and the untouched v go to slot_mapping[t] of the
+// pool [num_blocks, nkv, 16, hd].  The rotation is the one of hb_rope (cos/sin in f32,
+// rounded to T, apply_rope src/engine/arch/llama_tp.rs:112-152); K is cached after RoPE
+// (src/engine/arch/llama_tp.rs:242-259).
+template <typename T>
+__global__ void __launch_bounds__(kRkThreads)
+rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
+               const int32_t* __restrict__ positions, const int64_t* __restrict__ slots,
+               const float* __restrict__ inv_freq, int nq, int nkv, int hd, int64_t num_blocks) {
+  __shared__ float s_cos[256];
+  __shared__ float s_sin[256];
+  constexpr int N = Vec16<T>::N;
+  const int64_t t = blockIdx.x;
+  const int half = hd >> 1;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += kRkThreads) {
+    float s, c;
+    sincosf(pos * inv_freq[i], &s, &c);
+    s_cos[i] = to_f32<T>(from_f32<T>(c));
+    s_sin[i] = to_f32<T>(from_f32<T>(s));
+  }
+  __syncthreads();
+  const int64_t row_len = (int64_t)(nq + 2 * nkv) * hd;
+  T* row = qkv + t * row_len;
+  const int64_t slot = slots[t];
+  const bool store = slot >= 0 && slot < num_blocks * HB_BLOCK_SIZE;
+  const int64_t blk = store ? slot / HB_BLOCK_SIZE : 0, off = store ? slot % HB_BLOCK_SIZE : 0;
+  const int vph = half / N;  // vector pairs per head
+  // q heads and k heads: rotate
+  for (int idx = threadIdx.x; idx < (nq + nkv) * vph; idx += kRkThreads) {
+    const int h = idx / vph, v = idx % vph;
+    T* base = row + (int64_t)h * hd;  // k heads follow the q heads directly
+    Vec16<T> a, b;
+    a.load(base + v * N);
+    b.load(base + half + v * N);
+    float x1[N], x2[N], o1[N], o2[N];
+    a.unpack(x1);
+    b.unpack(x2);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const float c = s_cos[v * N + j], s = s_sin[v * N + j];
+      o1[j] = x1[j] * c - x2[j] * s;
+      o2[j] = x1[j] * s + x2[j] * c;
+    }
+    a.pack(o1);
+    b.pack(o2);
+    if (h < nq) {
+      a.store(base + v * N);
+      b.store(base + half + v * N);
+    } else if (store) {
+      T* dst = kc + (((blk * nkv + (h - nq)) * HB_BLOCK_SIZE + off) * (int64_t)hd);
+      a.store(dst + v * N);
+      b.store(dst + half + v * N);
+    }
+  }
+  // v heads: copy
+  if (store) {
+    const int vecs = hd / N;
+    for (int idx = threadIdx.x; idx < nkv * vecs; idx += kRkThreads) {
+      const int h = idx / vecs, v = idx % vecs;
+      Vec16<T> a;
+      a.load(row + (int64_t)(nq + nkv + h) * hd + v * N);
+      a.store(vc + (((blk * nkv + h) * HB_BLOCK_SIZE + off) * (int64_t)hd) + v * N);
+    }
+  }
+}
+
+int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
+                  const int32_t* positions, const int64_t* slot_mapping, const float* inv_freq,
+                  int64_t n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
+                  int64_t num_blocks, hb_dtype dtype) {
+  if (n_tokens == 0) return HB_OK;
+  if (head_dim % 2 || head_dim / 2 > 256)
+    return fail(HB_ERR_INVALID_ARG, "rope_kv_write: head_dim %d unsupported", head_dim);
+  HB_DISPATCH_DTYPE(dtype, T, {
+    if ((head_dim / 2) % Vec16<T>::N != 0)
+      return fail(HB_ERR_INVALID_ARG, "rope_kv_write: head_dim %d too small for 128-bit vectors",
+                  head_dim);
+    rope_kv_kernel<T><<<(unsigned)n_tokens, kRkThreads, 0, st>>>(
+        (T*)qkv, (T*)k_cache, (T*)v_cache, positions, slot_mapping, inv_freq, n_q_heads, n_kv_heads,
+        head_dim, num_blocks);
+  });
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// ------------------------------------------------------------ weight initialisation
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ dst, int64_t rows, int64_t cols, int64_t row0,
+                                   int64_t col0, int64_t g_cols, uint64_t key, float std) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * cols) return;
+  const int64_t r = idx / cols, c = idx % cols;
+  const uint64_t g = (uint64_t)((row0 + r) * g_cols + (col0 + c));
+  const uint64_t z = splitmix64(key ^ splitmix64(g));
+  const float u1 = ((float)(z >> 40) + 1.0f) * (1.0f / 16777216.0f);        // (0, 1]
+  const float u2 = ((float)((z >> 16) & 0xFFFFFF) + 0.5f) * (1.0f / 16777216.0f);
+  const float n = sqrtf(-2.0f * __logf(u1)) * __cosf(6.28318530717958647692f * u2);
+  dst[idx] = from_f32<T>(n * std);
+}
+
+template <typename T>
+__global__ void fill_const_kernel(T* __restrict__ dst, int64_t n, float v) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) dst[idx] = from_f32<T>(v);
+}
+
+template <typename T>
+__global__ void to_f32_kernel(float* __restrict__ dst, const T* __restrict__ src, int64_t n) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) dst[idx] = to_f32<T>(src[idx]);
+}
+
+int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
+                int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
+                float std) {
+  const int64_t n = rows * cols;
+  if (n == 0) return HB_OK;
+  const uint64_t key = seed * 0xD1342543DE82EF95ull + tensor_id * 0x9E3779B97F4A7C15ull + 1;
+  HB_DISPATCH_DTYPE(dtype, T, {
+    fill_normal_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((T*)dst, rows, cols, row0,
+                                                                      col0, g_cols, key, std);
+  });
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+int fill_const(cudaStream_t st, void* dst, hb_dtype dtype, int64_t n, float value) {
+  if (n == 0) return HB_OK;
+  HB_DISPATCH_DTYPE(dtype, T, {
+    fill_const_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((T*)dst, n, value);
+  });
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n) {
+  if (n == 0) return HB_OK;
+  HB_DISPATCH_DTYPE(dtype, T, {
+    to_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, (const T*)src, n);
+  });
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+}  // namespace hb

@@ -1,0 +1,754 @@
+// The decode-step engine behind hb_engine_* / hb_seq_* / hb_forward / hb_decode_batch.
+//
+// It stands where Engine (src/engine/loader.rs:66-339) -> Backend
+// (src/engine/arch/mod.rs:33-118) -> TpLlamaBackend (src/engine/arch/llama_tp.rs) stand
+// in the reference, with these differences of structure:
+//   - one engine object per rank (the reference loops over ranks inside one process,
+//     llama_tp.rs:506-576); with a multi-rank hb_world every rank runs the same step
+//     and the row-parallel partials meet in the peer-memory all-reduce;
+//   - B sequences per step through batched GEMMs and a paged KV pool, each sequence with
+//     a real block table (the reference decodes sequence by sequence over one shared,
+//     cat-grown cache: src/worker/mod.rs:280-293, llama_tp.rs:245-259);
+//   - no allocation and no host round trip inside a step: all buffers are created at
+//     load, the step is captured once per batch size into a CUDA graph and replayed.
+#include <cmath>
+#include <deque>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "comm.h"
+#include "common.h"
+#include "gemm.h"
+#include "json.h"
+#include "ops.h"
+#include "safetensors.h"
+
+struct hb_seq {
+  uint64_t id = 0;
+  std::vector<int64_t> blocks;  // physical block ids, table[pos / 16]
+  int64_t len = 0;              // tokens whose K/V are in the pool
+};
+
+namespace hb {
+
+struct LayerWeights {
+  void* wqkv = nullptr;   // [(hq_l + 2*hkv_l) * hd, H]   rows: q | k | v (column-parallel)
+  void* wo = nullptr;     // [H, hq_l * hd]               (row-parallel)
+  void* wgu = nullptr;    // [2 * I_l, H]                 rows: gate | up (column-parallel)
+  void* wdown = nullptr;  // [H, I_l]                     (row-parallel)
+  void* norm_in = nullptr;
+  void* norm_post = nullptr;
+};
+
+struct NamedTensor {
+  void* ptr;
+  int64_t rows, cols;
+};
+
+enum GemmKind { kQkv = 0, kO = 1, kGateUp = 2, kDown = 3, kLmHead = 4 };
+
+struct StepPlans {
+  std::vector<TcGemmPlan> layer;  // [L * 4]
+  TcGemmPlan lm_head;
+  int attn_splits = 1;
+  int64_t launches = 0;  // kernels in one step (fixed per batch size)
+  cudaGraphExec_t graph = nullptr;
+};
+
+}  // namespace hb
+
+struct hb_engine {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  hb_world* world = nullptr;
+  int rank = 0, ws = 1;
+  hb_dtype dtype = HB_BF16;
+  size_t es = 2;
+  // shape
+  int64_t H = 0, I = 0, L = 0, hq = 0, hkv = 0, hd = 0, V = 0;
+  double eps = 1e-5, theta = 10000.0;
+  int64_t hq_l = 0, hkv_l = 0, I_l = 0, qkv_rows = 0;
+  // weights
+  void* embed = nullptr;
+  void* lm_head = nullptr;
+  void* final_norm = nullptr;
+  std::vector<hb::LayerWeights> layers;
+  std::map<std::string, hb::NamedTensor> named;
+  std::vector<void*> allocations;
+  // KV pool
+  int64_t num_blocks = 0;
+  std::vector<void*> kc, vc;
+  std::deque<int64_t> free_blocks;  // FIFO: pop front / push back (block_manager.rs:58,63-83)
+  uint64_t next_seq_id = 0;
+  // step buffers
+  int max_batch = 0;
+  int64_t max_blocks_per_seq = 0;
+  uint8_t* d_inputs = nullptr;  // [ids | positions | ctx | pad | slots | tables]
+  uint8_t* h_inputs = nullptr;  // pinned mirror
+  size_t inputs_bytes = 0;
+  size_t off_ids = 0, off_pos = 0, off_ctx = 0, off_slots = 0, off_tables = 0;
+  void *d_h = nullptr, *d_x = nullptr, *d_qkv = nullptr, *d_attn = nullptr, *d_gu = nullptr,
+       *d_act = nullptr, *d_proj = nullptr;
+  float* d_logits = nullptr;
+  uint32_t* d_next = nullptr;
+  uint32_t* h_next = nullptr;  // pinned
+  float* d_inv_freq = nullptr;
+  void* d_attn_ws = nullptr;
+  size_t attn_ws_bytes = 0;
+  void* d_gemm_ws = nullptr;
+  size_t gemm_ws_bytes = 0;
+  int* d_err = nullptr;
+  bool use_tc = false, use_graph = true, fused_swiglu = true;
+  std::map<int, hb::StepPlans> plans;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = -1.f;
+  int64_t last_launches = 0;
+};
+
+namespace hb {
+
+// ------------------------------------------------------------------ host helpers
+static int dev_alloc(hb_engine* e, void** p, size_t bytes) {
+  HB_CUDA_CHECK(cudaMalloc(p, bytes ? bytes : 16));
+  e->allocations.push_back(*p);
+  return HB_OK;
+}
+
+static float src_to_f32(const uint8_t* p, const std::string& dt, int64_t i) {
+  if (dt == "F32") { float v; memcpy(&v, p + 4 * i, 4); return v; }
+  if (dt == "F16") { __half v; memcpy(&v, p + 2 * i, 2); return __half2float(v); }
+  uint16_t b; memcpy(&b, p + 2 * i, 2);  // BF16
+  uint32_t u = (uint32_t)b << 16; float v; memcpy(&v, &u, 4); return v;
+}
+
+static void f32_to_dst(uint8_t* d, hb_dtype dt, int64_t i, float v) {
+  if (dt == HB_F32) memcpy(d + 4 * i, &v, 4);
+  else if (dt == HB_F16) { __half h = __float2half_rn(v); memcpy(d + 2 * i, &h, 2); }
+  else { __nv_bfloat16 h = __float2bfloat16_rn(v); memcpy(d + 2 * i, &h, 2); }
+}
+
+static bool same_dtype(const std::string& s, hb_dtype d) {
+  return (s == "F32" && d == HB_F32) || (s == "F16" && d == HB_F16) || (s == "BF16" && d == HB_BF16);
+}
+
+// Copy rows [r0, r0+nr) x cols [c0, c0+nc) of a host [rows, cols] tensor to device
+// memory at dst (row-major [nr, nc]) converting to the engine dtype — the narrow() of
+// column_shard / row_shard (src/parallel/shard.rs:46-74) followed by to_device.
+static int upload_slice(hb_engine* e, void* dst, const StTensor& t, int64_t cols, int64_t r0,
+                        int64_t nr, int64_t c0, int64_t nc, std::vector<uint8_t>* scratch) {
+  scratch->resize((size_t)nr * nc * e->es);
+  uint8_t* s = scratch->data();
+  if (same_dtype(t.dtype, e->dtype)) {
+    for (int64_t r = 0; r < nr; ++r)
+      memcpy(s + (size_t)r * nc * e->es, t.data + ((size_t)(r0 + r) * cols + c0) * e->es, (size_t)nc * e->es);
+  } else {
+    for (int64_t r = 0; r < nr; ++r)
+      for (int64_t c = 0; c < nc; ++c)
+        f32_to_dst(s, e->dtype, r * nc + c, src_to_f32(t.data, t.dtype, (r0 + r) * cols + c0 + c));
+  }
+  HB_CUDA_CHECK(cudaMemcpy(dst, s, scratch->size(), cudaMemcpyHostToDevice));
+  return HB_OK;
+}
+
+static int check_divisibility(const hb_engine* e) {
+  // TpLlamaBackend::load (src/engine/arch/llama_tp.rs:407-427)
+  const int n = e->ws;
+  if (e->hq % n)
+    return fail(HB_ERR_NOT_DIVISIBLE,
+                "num_attention_heads (%lld) must be divisible by tensor_parallel_size (%d)",
+                (long long)e->hq, n);
+  if (e->hkv % n)
+    return fail(HB_ERR_NOT_DIVISIBLE,
+                "num_key_value_heads (%lld) must be divisible by tensor_parallel_size (%d)",
+                (long long)e->hkv, n);
+  if (e->I % n)
+    return fail(HB_ERR_NOT_DIVISIBLE,
+                "intermediate_size (%lld) must be divisible by tensor_parallel_size (%d)",
+                (long long)e->I, n);
+  return HB_OK;
+}
+
+static int setup_common(hb_engine* e, const hb_model_config* cfg, hb_world* world) {
+  const int tp = cfg->tensor_parallel_size > 0 ? cfg->tensor_parallel_size : 1;
+  e->world = world;
+  e->ws = world ? world->ws : 1;
+  e->rank = world ? world->rank : 0;
+  if (tp != e->ws)
+    return fail(HB_ERR_INVALID_ARG,
+                "tensor_parallel_size=%d but the world handed to the engine has %d rank(s)", tp, e->ws);
+  if (world) e->device = world->device;
+  else HB_CUDA_CHECK(cudaGetDevice(&e->device));
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
+  e->dtype = cfg->force_f32 ? HB_F32 : (cfg->bf16 ? HB_BF16 : HB_F16);  // src/engine/dtype.rs:22-28
+  e->es = dtype_size(e->dtype);
+  HB_CUDA_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+  HB_CUDA_CHECK(cudaEventCreate(&e->ev0));
+  HB_CUDA_CHECK(cudaEventCreate(&e->ev1));
+  const char* g = getenv("HB_NO_GRAPH");
+  e->use_graph = !(g && g[0] == '1');
+  return HB_OK;
+}
+
+static int setup_shape(hb_engine* e, const hb_model_shape& s) {
+  e->H = s.hidden_size; e->I = s.intermediate_size; e->L = s.num_hidden_layers;
+  e->hq = s.num_attention_heads;
+  e->hkv = s.num_key_value_heads == 0 ? s.num_attention_heads : s.num_key_value_heads;  // llama_tp.rs:81-87
+  e->V = s.vocab_size;
+  e->eps = s.rms_norm_eps; e->theta = s.rope_theta;
+  if (e->H <= 0 || e->I <= 0 || e->L <= 0 || e->hq <= 0 || e->V <= 0 || e->H % e->hq)
+    return fail(HB_ERR_INVALID_ARG, "bad model shape");
+  e->hd = e->H / e->hq;  // llama_tp.rs:77-79
+  int rc = check_divisibility(e);
+  if (rc) return rc;
+  e->hq_l = e->hq / e->ws; e->hkv_l = e->hkv / e->ws; e->I_l = e->I / e->ws;
+  e->qkv_rows = (e->hq_l + 2 * e->hkv_l) * e->hd;
+  const char* g = getenv("HB_GEMM");
+  const bool want_simt = g && std::string(g) == "simt";
+  e->use_tc = !want_simt && e->dtype == HB_BF16 && e->H % 64 == 0 && (e->hq_l * e->hd) % 64 == 0 &&
+              e->I_l % 64 == 0;
+  return HB_OK;
+}
+
+static int alloc_weights(hb_engine* e) {
+  const size_t es = e->es;
+  int rc;
+  if ((rc = dev_alloc(e, &e->embed, (size_t)e->V * e->H * es))) return rc;
+  if ((rc = dev_alloc(e, &e->lm_head, (size_t)e->V * e->H * es))) return rc;
+  if ((rc = dev_alloc(e, &e->final_norm, (size_t)e->H * es))) return rc;
+  e->layers.resize(e->L);
+  for (auto& l : e->layers) {
+    if ((rc = dev_alloc(e, &l.wqkv, (size_t)e->qkv_rows * e->H * es))) return rc;
+    if ((rc = dev_alloc(e, &l.wo, (size_t)e->H * e->hq_l * e->hd * es))) return rc;
+    if ((rc = dev_alloc(e, &l.wgu, (size_t)2 * e->I_l * e->H * es))) return rc;
+    if ((rc = dev_alloc(e, &l.wdown, (size_t)e->H * e->I_l * es))) return rc;
+    if ((rc = dev_alloc(e, &l.norm_in, (size_t)e->H * es))) return rc;
+    if ((rc = dev_alloc(e, &l.norm_post, (size_t)e->H * es))) return rc;
+  }
+  // names as the reference looks them up (llama_tp.rs:451-462,482-488), sharded shapes
+  e->named["model.embed_tokens.weight"] = {e->embed, e->V, e->H};
+  e->named["lm_head.weight"] = {e->lm_head, e->V, e->H};
+  e->named["model.norm.weight"] = {e->final_norm, 1, e->H};
+  for (int64_t i = 0; i < e->L; ++i) {
+    const std::string pf = "model.layers." + std::to_string(i);
+    auto& l = e->layers[i];
+    uint8_t* qkv = (uint8_t*)l.wqkv;
+    const size_t rowb = (size_t)e->H * es;
+    e->named[pf + ".self_attn.q_proj.weight"] = {qkv, e->hq_l * e->hd, e->H};
+    e->named[pf + ".self_attn.k_proj.weight"] = {qkv + (size_t)e->hq_l * e->hd * rowb, e->hkv_l * e->hd, e->H};
+    e->named[pf + ".self_attn.v_proj.weight"] = {qkv + (size_t)(e->hq_l + e->hkv_l) * e->hd * rowb, e->hkv_l * e->hd, e->H};
+    e->named[pf + ".self_attn.o_proj.weight"] = {l.wo, e->H, e->hq_l * e->hd};
+    e->named[pf + ".mlp.gate_proj.weight"] = {l.wgu, e->I_l, e->H};
+    e->named[pf + ".mlp.up_proj.weight"] = {(uint8_t*)l.wgu + (size_t)e->I_l * rowb, e->I_l, e->H};
+    e->named[pf + ".mlp.down_proj.weight"] = {l.wdown, e->H, e->I_l};
+    e->named[pf + ".input_layernorm.weight"] = {l.norm_in, 1, e->H};
+    e->named[pf + ".post_attention_layernorm.weight"] = {l.norm_post, 1, e->H};
+  }
+  return HB_OK;
+}
+
+static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
+  int rc;
+  e->max_batch = cfg->max_batch > 0 ? cfg->max_batch : 256;
+  const int64_t max_seq = cfg->max_seq_len > 0 ? (int64_t)cfg->max_seq_len : 2048;
+  e->max_blocks_per_seq = (max_seq + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
+  e->num_blocks = cfg->num_kv_blocks > 0 ? cfg->num_kv_blocks : e->max_blocks_per_seq * e->max_batch;
+  const size_t blk_bytes = (size_t)e->hkv_l * HB_BLOCK_SIZE * e->hd * e->es;
+  e->kc.resize(e->L); e->vc.resize(e->L);
+  for (int64_t l = 0; l < e->L; ++l) {
+    if ((rc = dev_alloc(e, &e->kc[l], blk_bytes * e->num_blocks))) return rc;
+    if ((rc = dev_alloc(e, &e->vc[l], blk_bytes * e->num_blocks))) return rc;
+    // unwritten slots are read (and masked) by the attention kernel: keep them finite
+    HB_CUDA_CHECK(cudaMemset(e->kc[l], 0, blk_bytes * e->num_blocks));
+    HB_CUDA_CHECK(cudaMemset(e->vc[l], 0, blk_bytes * e->num_blocks));
+  }
+  for (int64_t b = 0; b < e->num_blocks; ++b) e->free_blocks.push_back(b);
+
+  const int B = e->max_batch;
+  auto align16 = [](size_t v) { return (v + 15) / 16 * 16; };
+  e->off_ids = 0;
+  e->off_pos = align16(e->off_ids + (size_t)B * 4);
+  e->off_ctx = align16(e->off_pos + (size_t)B * 4);
+  e->off_slots = align16(e->off_ctx + (size_t)B * 4);
+  e->off_tables = align16(e->off_slots + (size_t)B * 8);
+  e->inputs_bytes = align16(e->off_tables + (size_t)B * e->max_blocks_per_seq * 4);
+  if ((rc = dev_alloc(e, (void**)&e->d_inputs, e->inputs_bytes))) return rc;
+  HB_CUDA_CHECK(cudaMallocHost((void**)&e->h_inputs, e->inputs_bytes));
+  HB_CUDA_CHECK(cudaMallocHost((void**)&e->h_next, (size_t)B * 4));
+  const size_t es = e->es;
+  if ((rc = dev_alloc(e, &e->d_h, (size_t)B * e->H * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_x, (size_t)B * e->H * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_qkv, (size_t)B * e->qkv_rows * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_attn, (size_t)B * e->hq_l * e->hd * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_gu, (size_t)B * 2 * e->I_l * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_act, (size_t)B * e->I_l * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_proj, (size_t)B * e->H * es))) return rc;
+  if ((rc = dev_alloc(e, (void**)&e->d_logits, (size_t)B * e->V * 4))) return rc;
+  if ((rc = dev_alloc(e, (void**)&e->d_next, (size_t)B * 4))) return rc;
+  if ((rc = dev_alloc(e, (void**)&e->d_err, 16))) return rc;
+  HB_CUDA_CHECK(cudaMemset(e->d_err, 0, 16));
+  std::vector<float> inv(e->hd / 2);
+  if ((rc = hb_rope_inv_freq((float)e->theta, (int)e->hd, inv.data()))) return rc;
+  if ((rc = dev_alloc(e, (void**)&e->d_inv_freq, inv.size() * 4))) return rc;
+  HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
+  e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
+  if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
+  return HB_OK;
+}
+
+// ------------------------------------------------------------------ step
+static int pick_attn_splits(const hb_engine* e, int B) {
+  DeviceInfo di;
+  if (device_info(e->device, &di)) return 1;
+  const int64_t units = (int64_t)B * e->hkv_l;
+  int s = (int)((2 * (int64_t)di.sm_count + units - 1) / units);
+  return std::max(1, std::min(s, 16));
+}
+
+static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
+  auto it = e->plans.find(B);
+  if (it != e->plans.end()) { *out = &it->second; return HB_OK; }
+  StepPlans sp;
+  sp.attn_splits = pick_attn_splits(e, B);
+  size_t ws = 0;
+  if (e->use_tc) {
+    sp.layer.resize(e->L * 4);
+    int rc;
+    for (int64_t l = 0; l < e->L; ++l) {
+      auto& w = e->layers[l];
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kQkv], e->d_x, w.wqkv, B, e->qkv_rows, e->H, kEpiStore, false, e->device))) return rc;
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kO], e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, kEpiStore, false, e->device))) return rc;
+      if (e->fused_swiglu) {
+        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_l, e->H, kEpiSwiGLU, false, e->device))) return rc;
+      } else {
+        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_l, e->H, kEpiStore, false, e->device))) return rc;
+      }
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_l, kEpiStore, false, e->device))) return rc;
+      for (int k = 0; k < 4; ++k) ws = std::max(ws, sp.layer[l * 4 + k].workspace_bytes());
+    }
+    if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
+    ws = std::max(ws, sp.lm_head.workspace_bytes());
+  }
+  if (ws > e->gemm_ws_bytes) {
+    // grows only when a new batch size needs more; never inside a captured step
+    void* p = nullptr;
+    HB_CUDA_CHECK(cudaMalloc(&p, ws));
+    HB_CUDA_CHECK(cudaMemset(p, 0, ws));
+    e->allocations.push_back(p);
+    e->d_gemm_ws = p;
+    e->gemm_ws_bytes = ws;
+    // plans made for other batch sizes keep pointing at buffers that stay allocated
+    for (auto& kv : e->plans)
+      if (kv.second.graph) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
+  }
+  auto ins = e->plans.emplace(B, std::move(sp));
+  *out = &ins.first->second;
+  return HB_OK;
+}
+
+static int run_gemm(hb_engine* e, StepPlans* sp, int64_t l, int kind, void* Y, const void* X,
+                    const void* W, int B, int64_t N, int64_t K, bool out_f32) {
+  ++e->last_launches;
+  if (e->use_tc) {
+    const TcGemmPlan& pl = (kind == kLmHead) ? sp->lm_head : sp->layer[l * 4 + kind];
+    return gemm_tc_run(pl, e->stream, Y, pl.N, e->d_gemm_ws, e->d_err);
+  }
+  return gemm_simt(e->stream, Y, X, W, B, N, K, e->dtype, out_f32);
+}
+
+// Issues every kernel of one decode step on e->stream (captured or direct).
+static int issue_step(hb_engine* e, StepPlans* sp, int B) {
+  int rc;
+  cudaStream_t st = e->stream;
+  const uint32_t* d_ids = (const uint32_t*)(e->d_inputs + e->off_ids);
+  const int32_t* d_pos = (const int32_t*)(e->d_inputs + e->off_pos);
+  const int32_t* d_ctx = (const int32_t*)(e->d_inputs + e->off_ctx);
+  const int64_t* d_slots = (const int64_t*)(e->d_inputs + e->off_slots);
+  const int32_t* d_tables = (const int32_t*)(e->d_inputs + e->off_tables);
+  const float eps = (float)e->eps;
+  e->last_launches = 0;
+
+  // h = embed[ids]; x = norm(h; w_in[0])                       llama_tp.rs:508-522
+  if ((rc = hb_embed(st, e->d_h, e->embed, d_ids, B, e->H, e->V, e->dtype))) return rc;
+  if ((rc = hb_rms_norm(st, e->d_x, e->d_h, e->layers[0].norm_in, B, e->H, eps, e->dtype))) return rc;
+  e->last_launches += 2;
+  for (int64_t l = 0; l < e->L; ++l) {
+    auto& w = e->layers[l];
+    // q|k|v = x . Wqkv^T                                      llama_tp.rs:232-234
+    if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false))) return rc;
+    // RoPE + KV append                                        llama_tp.rs:242-259
+    if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
+                            (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;
+    // softmax(q k^T / sqrt d) v over the block table          llama_tp.rs:264-324
+    if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
+                              d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
+                              e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
+                              e->dtype))) return rc;
+    e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
+    // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
+    if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
+    if (e->ws > 1) {
+      if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+      ++e->last_launches;
+    }
+    if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
+    ++e->last_launches;
+    // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
+    if (e->use_tc && e->fused_swiglu) {
+      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
+    } else {
+      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
+      if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_l, e->dtype))) return rc;
+      ++e->last_launches;
+    }
+    if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_l, false))) return rc;
+    if (e->ws > 1) {
+      if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+      ++e->last_launches;
+    }
+    // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
+    const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
+    if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, nw, B, e->H, eps, e->dtype))) return rc;
+    ++e->last_launches;
+  }
+  // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
+  if ((rc = run_gemm(e, sp, 0, kLmHead, e->d_logits, e->d_x, e->lm_head, B, e->V, e->H, true))) return rc;
+  if ((rc = hb_argmax(st, e->d_next, e->d_logits, B, e->V, HB_F32))) return rc;
+  ++e->last_launches;
+  return HB_OK;
+}
+
+static int seq_ensure_block(hb_engine* e, hb_seq* s, int64_t pos) {
+  while ((int64_t)s->blocks.size() * HB_BLOCK_SIZE <= pos) {
+    if (e->free_blocks.empty())
+      return fail(HB_ERR_OOM_BLOCKS, "no free KV blocks (pool of %lld)", (long long)e->num_blocks);
+    if ((int64_t)s->blocks.size() >= e->max_blocks_per_seq)
+      return fail(HB_ERR_OOM_BLOCKS, "sequence exceeds max_seq_len (%lld tokens)",
+                  (long long)(e->max_blocks_per_seq * HB_BLOCK_SIZE));
+    s->blocks.push_back(e->free_blocks.front());
+    e->free_blocks.pop_front();
+  }
+  return HB_OK;
+}
+
+static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t* tokens,
+                       uint32_t* next_tokens, float* logits_out /* host [B, V] or null */) {
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
+  if (B <= 0 || B > e->max_batch)
+    return fail(HB_ERR_INVALID_ARG, "batch %d outside [1, %d]", B, e->max_batch);
+  int rc;
+  uint32_t* h_ids = (uint32_t*)(e->h_inputs + e->off_ids);
+  int32_t* h_pos = (int32_t*)(e->h_inputs + e->off_pos);
+  int32_t* h_ctx = (int32_t*)(e->h_inputs + e->off_ctx);
+  int64_t* h_slots = (int64_t*)(e->h_inputs + e->off_slots);
+  int32_t* h_tables = (int32_t*)(e->h_inputs + e->off_tables);
+  for (int b = 0; b < B; ++b) {
+    hb_seq* s = seqs[b];
+    if (!s) return fail(HB_ERR_INVALID_ARG, "null sequence at index %d", b);
+    for (int j = 0; j < b; ++j)
+      if (seqs[j] == s) return fail(HB_ERR_INVALID_ARG, "sequence repeated in one batch");
+    const int64_t pos = s->len;
+    if ((rc = seq_ensure_block(e, s, pos))) return rc;
+    h_ids[b] = tokens[b];
+    h_pos[b] = (int32_t)pos;
+    h_ctx[b] = (int32_t)(pos + 1);
+    h_slots[b] = s->blocks[pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + pos % HB_BLOCK_SIZE;
+    int32_t* row = h_tables + (size_t)b * e->max_blocks_per_seq;
+    for (size_t i = 0; i < s->blocks.size(); ++i) row[i] = (int32_t)s->blocks[i];
+  }
+  StepPlans* sp = nullptr;
+  if ((rc = ensure_plans(e, B, &sp))) return rc;
+  // only the used prefix of each region matters; one copy of the whole block is simplest
+  HB_CUDA_CHECK(cudaMemcpyAsync(e->d_inputs, e->h_inputs, e->inputs_bytes, cudaMemcpyHostToDevice, e->stream));
+  if (e->use_graph) {
+    if (!sp->graph) {
+      cudaGraph_t g = nullptr;
+      HB_CUDA_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+      rc = issue_step(e, sp, B);
+      sp->launches = e->last_launches;
+      cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+      if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+      if (ce != cudaSuccess) return fail(HB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+      ce = cudaGraphInstantiate(&sp->graph, g, 0);
+      cudaGraphDestroy(g);
+      if (ce != cudaSuccess) return fail(HB_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(ce));
+    }
+    e->last_launches = sp->launches;
+    HB_CUDA_CHECK(cudaEventRecord(e->ev0, e->stream));
+    HB_CUDA_CHECK(cudaGraphLaunch(sp->graph, e->stream));
+    HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
+  } else {
+    HB_CUDA_CHECK(cudaEventRecord(e->ev0, e->stream));
+    if ((rc = issue_step(e, sp, B))) return rc;
+    HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
+  }
+  HB_CUDA_CHECK(cudaMemcpyAsync(e->h_next, e->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (logits_out)
+    HB_CUDA_CHECK(cudaMemcpyAsync(logits_out, e->d_logits, (size_t)B * e->V * 4, cudaMemcpyDeviceToHost, e->stream));
+  int h_err = 0;
+  HB_CUDA_CHECK(cudaMemcpyAsync(&h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
+  HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
+  HB_CUDA_CHECK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  if (h_err) {
+    cudaMemsetAsync(e->d_err, 0, 4, e->stream);
+    return fail(HB_ERR_TIMEOUT, "a bounded device-side wait ran out during the decode step");
+  }
+  if (e->world && e->ws > 1) {
+    const int stw = hb_world_status(e->world);
+    if (stw) return fail(stw, "a peer did not arrive in the all-reduce of the decode step");
+  }
+  for (int b = 0; b < B; ++b) {
+    seqs[b]->len += 1;
+    if (next_tokens) next_tokens[b] = e->h_next[b];
+  }
+  return HB_OK;
+}
+
+}  // namespace hb
+
+// ------------------------------------------------------------------------- C ABI
+extern "C" {
+
+int hb_engine_free(hb_engine* e) {
+  if (!e) return HB_OK;
+  cudaSetDevice(e->device);
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  for (auto& kv : e->plans)
+    if (kv.second.graph) cudaGraphExecDestroy(kv.second.graph);
+  for (void* p : e->allocations) cudaFree(p);
+  if (e->h_inputs) cudaFreeHost(e->h_inputs);
+  if (e->h_next) cudaFreeHost(e->h_next);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+  return HB_OK;
+}
+
+int hb_engine_create_random(const hb_model_shape* shape, const hb_model_config* cfg,
+                            hb_world* world, uint64_t seed, float std, int norm_ones,
+                            hb_engine** out) {
+  HB_CHECK_ARG(shape && cfg && out, "hb_engine_create_random: null argument");
+  std::unique_ptr<hb_engine, int (*)(hb_engine*)> e(new hb_engine, hb_engine_free);
+  int rc;
+  if ((rc = hb::setup_common(e.get(), cfg, world))) return rc;
+  if ((rc = hb::setup_shape(e.get(), *shape))) return rc;
+  if ((rc = hb::alloc_weights(e.get()))) return rc;
+  hb_engine* g = e.get();
+  cudaStream_t st = g->stream;
+  const int r = g->rank;
+  // tensor ids: 0 embed, 1 lm_head, 2 final norm, 16 + 16*layer + k for layer tensors.
+  // Each rank draws its slice of the global tensor: rows for column-parallel weights,
+  // columns for row-parallel ones (src/parallel/shard.rs:46-74).
+  if ((rc = hb::fill_normal(st, g->embed, g->dtype, g->V, g->H, 0, 0, g->H, seed, 0, std))) return rc;
+  if ((rc = hb::fill_normal(st, g->lm_head, g->dtype, g->V, g->H, 0, 0, g->H, seed, 1, std))) return rc;
+  auto fill_norm = [&](void* p, uint64_t tid) {
+    return norm_ones ? hb::fill_const(st, p, g->dtype, g->H, 1.0f)
+                     : hb::fill_normal(st, p, g->dtype, 1, g->H, 0, 0, g->H, seed, tid, std);
+  };
+  if ((rc = fill_norm(g->final_norm, 2))) return rc;
+  const size_t rowb = (size_t)g->H * g->es;
+  for (int64_t l = 0; l < g->L; ++l) {
+    auto& w = g->layers[l];
+    const uint64_t t0 = 16 + 16 * (uint64_t)l;
+    const int64_t qr = g->hq_l * g->hd, kr = g->hkv_l * g->hd;
+    uint8_t* qkv = (uint8_t*)w.wqkv;
+    if ((rc = hb::fill_normal(st, qkv, g->dtype, qr, g->H, r * qr, 0, g->H, seed, t0 + 0, std))) return rc;
+    if ((rc = hb::fill_normal(st, qkv + (size_t)qr * rowb, g->dtype, kr, g->H, r * kr, 0, g->H, seed, t0 + 1, std))) return rc;
+    if ((rc = hb::fill_normal(st, qkv + (size_t)(qr + kr) * rowb, g->dtype, kr, g->H, r * kr, 0, g->H, seed, t0 + 2, std))) return rc;
+    if ((rc = hb::fill_normal(st, w.wo, g->dtype, g->H, qr, 0, r * qr, g->hq * g->hd, seed, t0 + 3, std))) return rc;
+    if ((rc = hb::fill_normal(st, w.wgu, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 4, std))) return rc;
+    if ((rc = hb::fill_normal(st, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 5, std))) return rc;
+    if ((rc = hb::fill_normal(st, w.wdown, g->dtype, g->H, g->I_l, 0, r * g->I_l, g->I, seed, t0 + 6, std))) return rc;
+    if ((rc = fill_norm(w.norm_in, t0 + 7))) return rc;
+    if ((rc = fill_norm(w.norm_post, t0 + 8))) return rc;
+  }
+  HB_CUDA_CHECK(cudaStreamSynchronize(st));
+  if ((rc = hb::alloc_runtime(g, cfg))) return rc;
+  *out = e.release();
+  return HB_OK;
+}
+
+int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out) {
+  HB_CHECK_ARG(cfg && out && cfg->model_path, "hb_engine_load: null argument");
+  std::unique_ptr<hb_engine, int (*)(hb_engine*)> e(new hb_engine, hb_engine_free);
+  int rc;
+  if ((rc = hb::setup_common(e.get(), cfg, world))) return rc;
+  const std::string dir = cfg->model_path;
+  std::string text;
+  if ((rc = hb::read_text_file(dir + "/config.json", &text))) return rc;
+  hb::Json root;
+  std::string err;
+  hb::JsonParser jp(text.data(), text.size());
+  if (!jp.parse(&root, &err)) return hb::fail(HB_ERR_IO, "config.json: %s", err.c_str());
+  const std::string mt = root.string_or("model_type", "llama");
+  if (mt != "llama" && mt != "mistral")
+    return hb::fail(HB_ERR_INVALID_ARG, "model_type '%s' is not served by this path (llama, mistral)", mt.c_str());
+  hb_model_shape sh;
+  sh.hidden_size = (int64_t)root.number_or("hidden_size", 0);
+  sh.intermediate_size = (int64_t)root.number_or("intermediate_size", 0);
+  sh.num_hidden_layers = (int64_t)root.number_or("num_hidden_layers", 0);
+  sh.num_attention_heads = (int64_t)root.number_or("num_attention_heads", 0);
+  sh.num_key_value_heads = (int64_t)root.number_or("num_key_value_heads", 0);
+  sh.vocab_size = (int64_t)root.number_or("vocab_size", 0);
+  sh.rms_norm_eps = root.number_or("rms_norm_eps", 1e-5);     // llama_tp.rs:68-70
+  sh.rope_theta = root.number_or("rope_theta", 10000.0);      // llama_tp.rs:71-73
+  if ((rc = hb::setup_shape(e.get(), sh))) return rc;
+  if ((rc = hb::alloc_weights(e.get()))) return rc;
+
+  std::vector<std::string> files;
+  if ((rc = hb::list_safetensors(dir, &files))) return rc;
+  std::vector<std::unique_ptr<hb::SafetensorsFile>> shards;
+  std::map<std::string, const hb::StTensor*> all;
+  for (auto& f : files) {
+    shards.emplace_back(new hb::SafetensorsFile);
+    if ((rc = shards.back()->open(f))) return rc;
+    for (auto& kv : shards.back()->tensors()) all[kv.first] = &kv.second;
+  }
+  hb_engine* g = e.get();
+  std::vector<uint8_t> scratch;
+  auto get = [&](const std::string& name, int64_t rows, int64_t cols, const hb::StTensor** t) -> int {
+    auto it = all.find(name);
+    if (it == all.end()) return hb::fail(HB_ERR_IO, "Weight not found: %s", name.c_str());  // llama_tp.rs:380-385
+    const hb::StTensor* s = it->second;
+    if (s->dtype != "F32" && s->dtype != "F16" && s->dtype != "BF16")
+      return hb::fail(HB_ERR_UNSUPPORTED_DTYPE, "%s has dtype %s", name.c_str(), s->dtype.c_str());
+    if (s->numel() != rows * cols)
+      return hb::fail(HB_ERR_IO, "%s has %lld elements, expected %lld x %lld", name.c_str(),
+                      (long long)s->numel(), (long long)rows, (long long)cols);
+    *t = s;
+    return HB_OK;
+  };
+  const int r = g->rank;
+  const hb::StTensor* t = nullptr;
+  if ((rc = get("model.embed_tokens.weight", g->V, g->H, &t))) return rc;
+  if ((rc = hb::upload_slice(g, g->embed, *t, g->H, 0, g->V, 0, g->H, &scratch))) return rc;
+  if ((rc = get("lm_head.weight", g->V, g->H, &t))) return rc;  // no tied-embedding fallback (llama_tp.rs:488)
+  if ((rc = hb::upload_slice(g, g->lm_head, *t, g->H, 0, g->V, 0, g->H, &scratch))) return rc;
+  if ((rc = get("model.norm.weight", 1, g->H, &t))) return rc;
+  if ((rc = hb::upload_slice(g, g->final_norm, *t, g->H, 0, 1, 0, g->H, &scratch))) return rc;
+  const size_t rowb = (size_t)g->H * g->es;
+  for (int64_t l = 0; l < g->L; ++l) {
+    const std::string pf = "model.layers." + std::to_string(l);
+    auto& w = g->layers[l];
+    const int64_t qr = g->hq_l * g->hd, kr = g->hkv_l * g->hd, qd = g->hq * g->hd;
+    uint8_t* qkv = (uint8_t*)w.wqkv;
+    if ((rc = get(pf + ".self_attn.q_proj.weight", qd, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, qkv, *t, g->H, r * qr, qr, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".self_attn.k_proj.weight", g->hkv * g->hd, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, qkv + (size_t)qr * rowb, *t, g->H, r * kr, kr, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".self_attn.v_proj.weight", g->hkv * g->hd, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, qkv + (size_t)(qr + kr) * rowb, *t, g->H, r * kr, kr, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".self_attn.o_proj.weight", g->H, qd, &t))) return rc;
+    if ((rc = hb::upload_slice(g, w.wo, *t, qd, 0, g->H, r * qr, qr, &scratch))) return rc;
+    if ((rc = get(pf + ".mlp.gate_proj.weight", g->I, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, w.wgu, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".mlp.up_proj.weight", g->I, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".mlp.down_proj.weight", g->H, g->I, &t))) return rc;
+    if ((rc = hb::upload_slice(g, w.wdown, *t, g->I, 0, g->H, r * g->I_l, g->I_l, &scratch))) return rc;
+    if ((rc = get(pf + ".input_layernorm.weight", 1, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, w.norm_in, *t, g->H, 0, 1, 0, g->H, &scratch))) return rc;
+    if ((rc = get(pf + ".post_attention_layernorm.weight", 1, g->H, &t))) return rc;
+    if ((rc = hb::upload_slice(g, w.norm_post, *t, g->H, 0, 1, 0, g->H, &scratch))) return rc;
+  }
+  if ((rc = hb::alloc_runtime(g, cfg))) return rc;
+  *out = e.release();
+  return HB_OK;
+}
+
+int64_t hb_engine_num_layers(const hb_engine* e) { return e ? e->L : -1; }
+int64_t hb_engine_vocab_size(const hb_engine* e) { return e ? e->V : -1; }
+int64_t hb_engine_hidden_size(const hb_engine* e) { return e ? e->H : -1; }
+int64_t hb_engine_param_count(const hb_engine* e) {
+  if (!e) return -1;
+  // Engine::param_count (src/engine/loader.rs:323-329)
+  const int64_t attn = 4 * e->H * e->H, ffn = 3 * e->H * e->I;
+  return e->V * e->H + e->L * (attn + ffn) + e->V * e->H;
+}
+int64_t hb_engine_num_free_blocks(const hb_engine* e) { return e ? (int64_t)e->free_blocks.size() : -1; }
+void* hb_engine_stream(hb_engine* e) { return e ? (void*)e->stream : nullptr; }
+float hb_engine_last_step_ms(hb_engine* e) { return e ? e->last_ms : -1.f; }
+int64_t hb_engine_last_step_launches(const hb_engine* e) { return e ? e->last_launches : -1; }
+
+double hb_engine_step_bytes(const hb_engine* e, const int32_t* ctx_lens, int64_t n_seqs) {
+  if (!e) return -1.0;
+  const double es = (double)e->es;
+  double w = 0.0;
+  w += (double)e->L * ((double)e->qkv_rows * e->H + (double)e->H * e->hq_l * e->hd +
+                       3.0 * (double)e->I_l * e->H + 2.0 * e->H) * es;
+  w += ((double)e->V * e->H + e->H) * es;    // lm_head + final norm
+  w += (double)n_seqs * e->H * es;            // embedding rows
+  double kv = 0.0;
+  for (int64_t i = 0; i < n_seqs; ++i)
+    kv += (double)(ctx_lens ? ctx_lens[i] : 0) * e->L * 2.0 * e->hkv_l * e->hd * es;  // read
+  kv += (double)n_seqs * e->L * 2.0 * e->hkv_l * e->hd * es;                           // write
+  return w + kv;
+}
+
+int64_t hb_engine_get_tensor(hb_engine* e, const char* name, float* out, int64_t cap) {
+  if (!e || !name) return HB_ERR_INVALID_ARG;
+  auto it = e->named.find(name);
+  if (it == e->named.end()) return hb::fail(HB_ERR_INVALID_ARG, "no tensor named %s", name);
+  const int64_t n = it->second.rows * it->second.cols;
+  if (!out) return n;
+  if (cap < n) return hb::fail(HB_ERR_INVALID_ARG, "buffer of %lld floats too small for %lld", (long long)cap, (long long)n);
+  cudaSetDevice(e->device);
+  float* tmp = nullptr;
+  if (cudaMalloc((void**)&tmp, (size_t)n * 4) != cudaSuccess) return hb::fail(HB_ERR_CUDA, "cudaMalloc failed");
+  int rc = hb::to_f32(e->stream, tmp, it->second.ptr, e->dtype, n);
+  if (!rc && cudaMemcpyAsync(out, tmp, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) rc = HB_ERR_CUDA;
+  cudaStreamSynchronize(e->stream);
+  cudaFree(tmp);
+  return rc ? rc : n;
+}
+
+int hb_seq_create(hb_engine* e, hb_seq** out) {
+  HB_CHECK_ARG(e && out, "hb_seq_create: null argument");
+  hb_seq* s = new hb_seq;
+  s->id = e->next_seq_id++;
+  *out = s;
+  return HB_OK;
+}
+
+int hb_seq_free(hb_engine* e, hb_seq* s) {
+  if (!s) return HB_OK;
+  HB_CHECK_ARG(e, "hb_seq_free: null engine");
+  for (int64_t b : s->blocks) e->free_blocks.push_back(b);
+  delete s;
+  return HB_OK;
+}
+
+int64_t hb_seq_len(const hb_seq* s) { return s ? s->len : -1; }
+
+int64_t hb_seq_block_table(const hb_seq* s, int64_t* out, int64_t cap) {
+  if (!s) return HB_ERR_INVALID_ARG;
+  for (size_t i = 0; i < s->blocks.size() && (int64_t)i < cap && out; ++i) out[i] = s->blocks[i];
+  return (int64_t)s->blocks.size();
+}
+
+int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,
+                    uint32_t* next_tokens, float* logits_opt) {
+  HB_CHECK_ARG(e && seqs && last_tokens, "hb_decode_batch: null argument");
+  return hb::decode_step(e, seqs, (int)B, last_tokens, next_tokens, logits_opt);
+}
+
+int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t seq_pos,
+               float* logits_out) {
+  if (n == 0) return hb::fail(HB_ERR_EMPTY, "hb_forward: token list is empty");
+  HB_CHECK_ARG(e && s && ids && logits_out, "hb_forward: null argument");
+  if ((int64_t)seq_pos != s->len)
+    return hb::fail(HB_ERR_INVALID_ARG, "hb_forward: seq_pos %zu but the sequence holds %lld tokens",
+                    seq_pos, (long long)s->len);
+  // Prefill is fed token by token through the decode step: causal attention over the
+  // growing cache equals the masked prefill of llama_tp.rs:313-316.
+  for (size_t i = 0; i < n; ++i) {
+    hb_seq* one[1] = {s};
+    int rc = hb::decode_step(e, one, 1, ids + i, nullptr, i + 1 == n ? logits_out : nullptr);
+    if (rc) return rc;
+  }
+  return HB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,50 @@
+// Internal GEMM interface: Y[M,N] = X[M,K] . W[N,K]^T (+ fused epilogues).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.h"
+
+namespace hb {
+
+// CUDA-core kernel, any dtype/shape.
+int gemm_simt(cudaStream_t st, void* Y, const void* X, const void* W, int64_t M, int64_t N,
+              int64_t K, hb_dtype dtype, bool out_f32);
+
+// What the tensor-core kernel does with the finished fp32 tile.
+enum TcEpilogue : int {
+  kEpiStore = 0,     // Y = acc (bf16, or f32 when out_f32)
+  kEpiSwiGLU = 1,    // W rows are [gate tile | up tile] pairs: Y = silu(gate) * up, N_out = N/2
+};
+
+// A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by
+// value to the kernel, so a plan can be replayed inside a CUDA graph.
+struct TcGemmPlan {
+  CUtensorMap tm_w;  // A operand: W [N, K], box 128 x 64
+  CUtensorMap tm_x;  // B operand: X [M, K], box m_pad x 64
+  int64_t M = 0, N = 0, K = 0;
+  int m_pad = 0;      // UMMA N (multiple of 16, <= 256)
+  int m_tiles = 0;    // ceil(M / m_pad)
+  int n_tiles = 0;    // ceil(N / 128)
+  int splits = 1;     // split-K factor
+  int stages = 0;
+  int tmem_cols = 0;
+  size_t smem_bytes = 0;
+  int epilogue = kEpiStore;
+  bool out_f32 = false;
+  // scratch layout inside the caller's workspace
+  size_t ws_partials_bytes = 0;  // fp32 [m_tiles*n_tiles*splits][m_pad][128]
+  size_t ws_counters_bytes = 0;  // int32 [m_tiles*n_tiles] (zero between calls)
+  size_t workspace_bytes() const { return ws_partials_bytes + ws_counters_bytes + 16; }
+};
+
+bool gemm_tc_supported(int64_t M, int64_t N, int64_t K, hb_dtype dtype);
+// X and W must be 16-byte aligned device pointers; they are baked into the plan.
+int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
+                 int epilogue, bool out_f32, int device, int force_splits = 0);
+// Y row stride ldy in elements.  workspace: plan.workspace_bytes(), zeroed once.
+// err_flag (device int, may be null) is set non-zero when a bounded wait ran out.
+int gemm_tc_run(const TcGemmPlan& plan, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
+                int* err_flag);
+
+}  // namespace hb

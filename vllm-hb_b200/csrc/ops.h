@@ -1,0 +1,30 @@
+// Internal launchers shared between the public kernel entry points and the engine.
+#pragma once
+
+#include "common.h"
+
+namespace hb {
+
+int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride, const void* k_cache,
+                    const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
+                    int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                    int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
+                    hb_dtype dtype);
+
+// RoPE on the q and k parts of a fused [q | k | v] projection row and the paged KV
+// write in one pass: q is rotated in place, rotated k and v go straight to their slot.
+int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
+                  const int32_t* positions, const int64_t* slot_mapping, const float* inv_freq,
+                  int64_t n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
+                  int64_t num_blocks, hb_dtype dtype);
+
+// Fill a [rows, cols] slice of a global [g_rows, g_cols] tensor with N(0, std) drawn
+// from a counter-based generator keyed by (seed, tensor id, global element index).
+int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
+                int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
+                float std);
+int fill_const(cudaStream_t st, void* dst, hb_dtype dtype, int64_t n, float value);
+// dst (f32) = src (dtype)
+int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n);
+
+}  // namespace hb
