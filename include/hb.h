@@ -138,6 +138,17 @@ size_t hb_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, hb_dtype dtype);
 int hb_gemm(void* stream, void* Y, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
             hb_dtype dtype, void* workspace);
 
+/* The same GEMM with the epilogues the decode step fuses into it (bf16, K%64==0 only):
+ *   epilogue 0: Y[M,N] = X.W^T, as bf16 or (out_f32 != 0) as fp32 — the logits GEMM;
+ *   epilogue 1: W = [gate (N/2 rows) ; up (N/2 rows)], Y[M,N/2] = silu(X.gate^T) * (X.up^T)
+ *               — gate, up, SiLU and the product of ffn_partial
+ *               (src/engine/arch/llama_tp.rs:333-338) in one kernel.
+ * force_splits > 0 overrides the split-K factor.  Workspace:
+ * hb_gemm_ex_workspace_bytes(), zero-initialised once. */
+size_t hb_gemm_ex_workspace_bytes(int64_t M, int64_t N, int64_t K, int epilogue, int force_splits);
+int hb_gemm_ex(void* stream, void* Y, const void* X, const void* W, int64_t M, int64_t N,
+               int64_t K, int epilogue, int out_f32, int force_splits, void* workspace);
+
 /* out[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i]; gate_up [M, 2*inter]
  * (src/engine/arch/llama_tp.rs:333-339). */
 int hb_silu_mul(void* stream, void* out, const void* gate_up, int64_t M, int64_t inter,
@@ -342,6 +353,16 @@ int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t se
  * [B, vocab]) may be NULL.  Copies in and out happen inside the call. */
 int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,
                     uint32_t* next_tokens, float* logits_opt);
+/* One decode step issued kernel by kernel (no graph) with CUDA events between the
+ * kernels: ms_by_kind receives HB_PROFILE_KINDS floats = device time spent in
+ * 0 GEMMs, 1 decode attention, 2 RoPE + KV write, 3 (add +) RMSNorm, 4 embedding /
+ * argmax / SwiGLU gate, 5 all-reduce.  The step counts like any other decode step. */
+#define HB_PROFILE_KINDS 6
+int hb_engine_profile_step(hb_engine* e, hb_seq* const* seqs, size_t B,
+                           const uint32_t* last_tokens, uint32_t* next_tokens, float* ms_by_kind);
+/* Algorithmic bytes all GEMM launches of one decode step move for batch B on this rank
+ * (weights + activations in + results out). */
+double hb_engine_gemm_bytes(const hb_engine* e, int64_t B);
 /* Device-time of the last hb_decode_batch kernels only (ms, CUDA events on the
  * engine's stream); negative if none. */
 float hb_engine_last_step_ms(hb_engine* e);

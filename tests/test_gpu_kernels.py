@@ -266,3 +266,45 @@ def test_argmax_first_maximum(hb, cuda):
     x[2, :] = -1.0                     # all equal -> 0
     got = hb.argmax(torch.from_numpy(x).to(cuda)).cpu().numpy()
     assert got.tolist() == np.argmax(x, axis=1).tolist()
+
+
+@pytest.mark.parametrize("M,I,K_", [(16, 1024, 512), (64, 14336, 4096), (128, 3584, 8192), (5, 688, 256)])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_gemm_swiglu_epilogue(hb, cuda, M, I, K_, splits):
+    """gate, up, SiLU and the product in the GEMM epilogue == the unfused sequence
+    (src/engine/arch/llama_tp.rs:333-338)."""
+    g = torch.Generator(device="cpu").manual_seed(I)
+    x = torch.randn(M, K_, generator=g).to(cuda, torch.bfloat16)
+    w = (torch.randn(2 * I, K_, generator=g) * 0.05).to(cuda, torch.bfloat16)
+    y = hb.gemm_ex(x, w, epilogue=1, force_splits=splits)
+    gu = x.float() @ w.float().T
+    want = (torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]).cpu().numpy()
+    assert rel_err(host(y), want) <= 2e-2
+
+
+@pytest.mark.parametrize("M,N,K_,splits", [(16, 2048, 512, 0), (64, 128256, 4096, 0), (16, 2048, 512, 2), (1, 384, 1024, 4)])
+def test_gemm_fp32_output(hb, cuda, M, N, K_, splits):
+    """The logits GEMM keeps the fp32 accumulator (no bf16 rounding of the result)."""
+    g = torch.Generator(device="cpu").manual_seed(N)
+    x = torch.randn(M, K_, generator=g).to(cuda, torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) * 0.02).to(cuda, torch.bfloat16)
+    y = hb.gemm_ex(x, w, epilogue=0, out_f32=True, force_splits=splits)
+    assert y.dtype == torch.float32
+    want = (x.float() @ w.float().T).cpu().numpy()
+    assert rel_err(host(y), want) <= 1e-3
+
+
+def test_gemm_shared_workspace_between_shapes(hb, cuda):
+    """Plans of different shapes may share one zero-initialised workspace back to back
+    (the decode step does): counters are left zeroed in a fixed place."""
+    shapes = [(16, 768, 512), (16, 2048, 512), (16, 512, 1024), (16, 2048, 512)]
+    code = hb.BF16
+    need = max(hb.lib.hb_gemm_ex_workspace_bytes(M, N, K_, 0, 2) for M, N, K_ in shapes)
+    ws = torch.zeros(need, dtype=torch.uint8, device=cuda)
+    for i, (M, N, K_) in enumerate(shapes * 2):
+        x = torch.randn(M, K_, device=cuda).to(torch.bfloat16)
+        w = (torch.randn(N, K_, device=cuda) * 0.02).to(torch.bfloat16)
+        y = torch.empty(M, N, device=cuda, dtype=torch.bfloat16)
+        hb.check(hb.lib.hb_gemm_ex(None, y.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K_, 0, 0, 2, ws.data_ptr()))
+        torch.cuda.synchronize()
+        assert rel_err(host(y), (x.float() @ w.float().T).cpu().numpy()) <= 2e-2, (i, M, N, K_)

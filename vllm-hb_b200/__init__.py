@@ -95,6 +95,8 @@ _SIGS = {
     "hb_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _vp, _i]),
     "hb_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
     "hb_gemm": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
+    "hb_gemm_ex_workspace_bytes": (_sz, [_i64, _i64, _i64, _i, _i]),
+    "hb_gemm_ex": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _vp]),
     "hb_silu_mul": (_i, [_vp, _vp, _vp, _i64, _i64, _i]),
     "hb_embed": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "hb_argmax": (_i, [_vp, _vp, _vp, _i64, _i64, _i]),
@@ -151,6 +153,8 @@ _SIGS = {
     "hb_seq_block_table": (_i64, [_vp, _vp, _i64]),
     "hb_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "hb_decode_batch": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "hb_engine_profile_step": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "hb_engine_gemm_bytes": (C.c_double, [_vp, _i64]),
     "hb_engine_last_step_ms": (_f, [_vp]),
     "hb_engine_last_step_launches": (_i64, [_vp]),
     "hb_engine_stream": (_vp, [_vp]),
@@ -319,6 +323,22 @@ def gemm(x, w, stream=None):
     ws_bytes = lib.hb_gemm_workspace_bytes(M, N, K, code)
     ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     check(lib.hb_gemm(_stream(stream), _ptr(y), _ptr(x), _ptr(w), M, N, K, code, _ptr(ws)))
+    return y
+
+
+def gemm_ex(x, w, epilogue: int = 0, out_f32: bool = False, force_splits: int = 0, stream=None):
+    """tcgen05 GEMM with a fused epilogue: 0 = store (bf16 or fp32), 1 = SwiGLU over
+    w = [gate ; up] giving [M, N/2]."""
+    import torch
+
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue == 1 else N
+    y = torch.empty((M, n_out), dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
+    ws_bytes = lib.hb_gemm_ex_workspace_bytes(M, N, K, epilogue, force_splits)
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    check(lib.hb_gemm_ex(_stream(stream), _ptr(y), _ptr(x), _ptr(w), M, N, K, epilogue, int(out_f32),
+                         force_splits, _ptr(ws)))
     return y
 
 
@@ -655,6 +675,21 @@ class Engine:
         check(lib.hb_decode_batch(self.handle, arr, B, last.ctypes.data, next_tokens.ctypes.data,
                                   logits.ctypes.data if logits is not None else None))
         return next_tokens
+
+    PROFILE_KINDS = ("gemm", "attention", "rope_kv", "norm", "other", "all_reduce")
+
+    def profile_step(self, seqs: Sequence[Sequence_], last_tokens: np.ndarray) -> tuple[np.ndarray, dict]:
+        """One eager decode step with per-kernel-kind device times (ms)."""
+        B = len(seqs)
+        arr = (C.c_void_p * B)(*[s.handle for s in seqs])
+        last = np.ascontiguousarray(np.asarray(last_tokens, dtype=np.uint32))
+        nxt = np.empty(B, dtype=np.uint32)
+        ms = np.zeros(len(self.PROFILE_KINDS), dtype=np.float32)
+        check(lib.hb_engine_profile_step(self.handle, arr, B, last.ctypes.data, nxt.ctypes.data, ms.ctypes.data))
+        return nxt, dict(zip(self.PROFILE_KINDS, ms.tolist()))
+
+    def gemm_bytes(self, batch: int) -> float:
+        return lib.hb_engine_gemm_bytes(self.handle, batch)
 
     def last_step_ms(self) -> float:
         return lib.hb_engine_last_step_ms(self.handle)

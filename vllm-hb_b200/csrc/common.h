@@ -24,9 +24,11 @@ inline bool dtype_valid(int d) { return d == HB_F32 || d == HB_F16 || d == HB_BF
 #define HB_CUDA_CHECK(expr)                                                              \
   do {                                                                                   \
     cudaError_t err__ = (expr);                                                          \
-    if (err__ != cudaSuccess)                                                            \
+    if (err__ != cudaSuccess) {                                                          \
+      cudaGetLastError(); /* clear the non-sticky error so later calls start clean */    \
       return ::hb::fail(HB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                     \
                         cudaGetErrorString(err__), __FILE__, __LINE__);                  \
+    }                                                                                    \
   } while (0)
 
 #define HB_CHECK_ARG(cond, ...)                                 \

@@ -105,6 +105,12 @@ struct hb_engine {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = -1.f;
   int64_t last_launches = 0;
+  // per-kernel-kind timing of one eager step (hb_engine_profile_step)
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;
+  std::vector<int> prof_cats;
+  size_t prof_used = 0;
+  float prof_ms[8] = {0};
 };
 
 namespace hb {
@@ -357,6 +363,20 @@ static int run_gemm(hb_engine* e, StepPlans* sp, int64_t l, int kind, void* Y, c
   return gemm_simt(e->stream, Y, X, W, B, N, K, e->dtype, out_f32);
 }
 
+enum ProfCat { kCatGemm = 0, kCatAttention = 1, kCatRopeKv = 2, kCatNorm = 3, kCatOther = 4, kCatComm = 5, kNumCats = 6 };
+
+// While profiling, every call opens a timed segment of kind `cat` on the stream.
+static void prof_mark(hb_engine* e, int cat) {
+  if (!e->profiling) return;
+  if (e->prof_used == e->prof_events.size()) {
+    cudaEvent_t ev = nullptr;
+    cudaEventCreate(&ev);
+    e->prof_events.push_back(ev);
+  }
+  cudaEventRecord(e->prof_events[e->prof_used++], e->stream);
+  e->prof_cats.push_back(cat);
+}
+
 // Issues every kernel of one decode step on e->stream (captured or direct).
 static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   int rc;
@@ -370,52 +390,68 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   e->last_launches = 0;
 
   // h = embed[ids]; x = norm(h; w_in[0])                       llama_tp.rs:508-522
+  prof_mark(e, kCatOther);
   if ((rc = hb_embed(st, e->d_h, e->embed, d_ids, B, e->H, e->V, e->dtype))) return rc;
+  prof_mark(e, kCatNorm);
   if ((rc = hb_rms_norm(st, e->d_x, e->d_h, e->layers[0].norm_in, B, e->H, eps, e->dtype))) return rc;
   e->last_launches += 2;
   for (int64_t l = 0; l < e->L; ++l) {
     auto& w = e->layers[l];
     // q|k|v = x . Wqkv^T                                      llama_tp.rs:232-234
+    prof_mark(e, kCatGemm);
     if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false))) return rc;
     // RoPE + KV append                                        llama_tp.rs:242-259
+    prof_mark(e, kCatRopeKv);
     if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
                             (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;
     // softmax(q k^T / sqrt d) v over the block table          llama_tp.rs:264-324
+    prof_mark(e, kCatAttention);
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
                               e->dtype))) return rc;
     e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
+    prof_mark(e, kCatGemm);
     if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
     if (e->ws > 1) {
+      prof_mark(e, kCatComm);
       if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
       ++e->last_launches;
     }
+    prof_mark(e, kCatNorm);
     if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
     ++e->last_launches;
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
+    prof_mark(e, kCatGemm);
     if (e->use_tc && e->fused_swiglu) {
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
     } else {
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
+      prof_mark(e, kCatOther);
       if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_l, e->dtype))) return rc;
       ++e->last_launches;
     }
+    prof_mark(e, kCatGemm);
     if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_l, false))) return rc;
     if (e->ws > 1) {
+      prof_mark(e, kCatComm);
       if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
       ++e->last_launches;
     }
     // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
     const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
+    prof_mark(e, kCatNorm);
     if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, nw, B, e->H, eps, e->dtype))) return rc;
     ++e->last_launches;
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
+  prof_mark(e, kCatGemm);
   if ((rc = run_gemm(e, sp, 0, kLmHead, e->d_logits, e->d_x, e->lm_head, B, e->V, e->H, true))) return rc;
+  prof_mark(e, kCatOther);
   if ((rc = hb_argmax(st, e->d_next, e->d_logits, B, e->V, HB_F32))) return rc;
   ++e->last_launches;
+  prof_mark(e, -1);  // closes the last segment
   return HB_OK;
 }
 
@@ -461,7 +497,7 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
   if ((rc = ensure_plans(e, B, &sp))) return rc;
   // only the used prefix of each region matters; one copy of the whole block is simplest
   HB_CUDA_CHECK(cudaMemcpyAsync(e->d_inputs, e->h_inputs, e->inputs_bytes, cudaMemcpyHostToDevice, e->stream));
-  if (e->use_graph) {
+  if (e->use_graph && !e->profiling) {
     if (!sp->graph) {
       cudaGraph_t g = nullptr;
       HB_CUDA_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
@@ -490,6 +526,16 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
   HB_CUDA_CHECK(cudaMemcpyAsync(&h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
   HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
   HB_CUDA_CHECK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  if (e->profiling) {
+    for (int c = 0; c < kNumCats; ++c) e->prof_ms[c] = 0.f;
+    for (size_t i = 0; i + 1 < e->prof_used; ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e->prof_events[i], e->prof_events[i + 1]);
+      if (e->prof_cats[i] >= 0 && e->prof_cats[i] < kNumCats) e->prof_ms[e->prof_cats[i]] += ms;
+    }
+    e->prof_used = 0;
+    e->prof_cats.clear();
+  }
   if (h_err) {
     cudaMemsetAsync(e->d_err, 0, 4, e->stream);
     return fail(HB_ERR_TIMEOUT, "a bounded device-side wait ran out during the decode step");
@@ -732,6 +778,29 @@ int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t*
                     uint32_t* next_tokens, float* logits_opt) {
   HB_CHECK_ARG(e && seqs && last_tokens, "hb_decode_batch: null argument");
   return hb::decode_step(e, seqs, (int)B, last_tokens, next_tokens, logits_opt);
+}
+
+int hb_engine_profile_step(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,
+                           uint32_t* next_tokens, float* ms_by_kind) {
+  HB_CHECK_ARG(e && seqs && last_tokens && ms_by_kind, "hb_engine_profile_step: null argument");
+  e->profiling = true;
+  int rc = hb::decode_step(e, seqs, (int)B, last_tokens, next_tokens, nullptr);
+  e->profiling = false;
+  if (rc) return rc;
+  for (int c = 0; c < HB_PROFILE_KINDS; ++c) ms_by_kind[c] = e->prof_ms[c];
+  return HB_OK;
+}
+
+double hb_engine_gemm_bytes(const hb_engine* e, int64_t B) {
+  if (!e) return -1.0;
+  const double es = (double)e->es, b = (double)B;
+  const double qkv = (double)e->qkv_rows, o_in = (double)e->hq_l * e->hd, H = (double)e->H,
+               Il = (double)e->I_l, V = (double)e->V;
+  double per_layer = (qkv * H + b * H + b * qkv) * es        // q|k|v projection
+                     + (H * o_in + b * o_in + b * H) * es    // o_proj
+                     + (2 * Il * H + b * H + b * Il) * es    // gate|up with the SwiGLU epilogue
+                     + (H * Il + b * Il + b * H) * es;       // down_proj
+  return (double)e->L * per_layer + (V * H + b * H) * es + b * V * 4.0;  // + lm_head, fp32 logits
 }
 
 int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t seq_pos,

@@ -35,3 +35,32 @@ int hb_gemm(void* stream, void* Y, const void* X, const void* W, int64_t M, int6
 }
 
 }  // extern "C"
+
+extern "C" {
+
+size_t hb_gemm_ex_workspace_bytes(int64_t M, int64_t N, int64_t K, int epilogue, int force_splits) {
+  if (!hb::gemm_tc_supported(M, N, K, HB_BF16)) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  hb::TcGemmPlan plan;
+  alignas(16) static char dummy[16];
+  if (hb::gemm_tc_plan(&plan, dummy, dummy, M, N, K, epilogue, false, dev, force_splits) != HB_OK) return 0;
+  return plan.workspace_bytes();
+}
+
+int hb_gemm_ex(void* stream, void* Y, const void* X, const void* W, int64_t M, int64_t N,
+               int64_t K, int epilogue, int out_f32, int force_splits, void* workspace) {
+  HB_CHECK_ARG(Y && X && W, "hb_gemm_ex: null pointer");
+  HB_CHECK_ARG(epilogue == hb::kEpiStore || epilogue == hb::kEpiSwiGLU, "hb_gemm_ex: unknown epilogue %d", epilogue);
+  HB_CHECK_ARG(hb::gemm_tc_supported(M, N, K, HB_BF16),
+               "hb_gemm_ex: bf16 with K %% 64 == 0 only (M=%lld N=%lld K=%lld)", (long long)M,
+               (long long)N, (long long)K);
+  int dev = 0;
+  HB_CUDA_CHECK(cudaGetDevice(&dev));
+  hb::TcGemmPlan plan;
+  int rc = hb::gemm_tc_plan(&plan, X, W, M, N, K, epilogue, out_f32 != 0, dev, force_splits);
+  if (rc) return rc;
+  return hb::gemm_tc_run(plan, (cudaStream_t)stream, Y, plan.N, workspace, nullptr);
+}
+
+}  // extern "C"

@@ -34,6 +34,7 @@ constexpr int kUmmaK = 16;
 constexpr int kMaxStages = 8;
 constexpr int kTcThreads = 128;
 constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr size_t kCounterBlockBytes = 64 * 1024;  // int32 counters of up to 16384 tiles
 
 struct TcParams {
   int M, N;                 // N = weight rows (for SwiGLU: rows of gate == rows of up)
@@ -435,8 +436,12 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   pl.splits = force_splits > 0 ? std::min(force_splits, k_chunks)
                                : pick_splits(pl.n_tiles * pl.m_tiles, k_chunks, slots);
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
+  // The tile counters sit in a block of FIXED size at the start of the workspace, so
+  // that plans of different shapes sharing one workspace never see each other's
+  // partials where they expect zeroed counters.
+  if (units * sizeof(int) > kCounterBlockBytes) pl.splits = 1;
   pl.ws_partials_bytes = pl.splits > 1 ? units * pl.splits * n_acc * pl.m_pad * kTileN * sizeof(float) : 0;
-  pl.ws_counters_bytes = pl.splits > 1 ? ((units * sizeof(int) + 15) / 16) * 16 : 0;
+  pl.ws_counters_bytes = pl.splits > 1 ? kCounterBlockBytes : 0;
   // opt in to the large dynamic shared memory window once per device (here, not at
   // launch, so that launches stay legal inside a stream capture)
   {
@@ -446,8 +451,9 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     if (cur >= 0 && cur < 64 && !dev_done[cur]) {
+      // 227 KiB per CTA minus the kernel's static shared memory (barriers, flags)
       HB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024));
+                                         226 * 1024));
       dev_done[cur] = true;
     }
   }
