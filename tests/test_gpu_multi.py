@@ -1,0 +1,167 @@
+"""Tensor-parallel pieces on 2+ GPUs of one box, driven from one process the way the
+reference drives its ranks (src/engine/arch/llama_tp.rs:506-576): the peer-memory
+all-reduce against the rank-order sum of src/parallel/comm.rs:47-62, and the fused
+row-parallel kernel against the unfused oracle.  Skipped on a single-GPU box."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kernels_ref as K
+from oracle import parallel_ref as P
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+TORCH = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def worlds(hb):
+    n = min(hb.device_count(), 8)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 1 << (n.bit_length() - 1)  # 2, 4 or 8
+    ws = hb.TpWorld.new_local(n, staging_bytes=64 << 20)
+    yield ws
+    for w in ws:
+        w.close()
+
+
+def on_all(worlds, fn):
+    outs = []
+    for r, w in enumerate(worlds):
+        with torch.cuda.device(w.device()):
+            outs.append(fn(r, w))
+    for w in worlds:
+        torch.cuda.synchronize(w.device())
+    return outs
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32", "f16"])
+@pytest.mark.parametrize("count", [8, 8192, 128 * 8192, 40 * 1000])
+@pytest.mark.parametrize("algo", ["one_shot", "two_shot", "auto"])
+def test_all_reduce(hb, worlds, dtype, count, algo):
+    R = len(worlds)
+    code = {"one_shot": hb.ALGO_ONE_SHOT, "two_shot": hb.ALGO_TWO_SHOT, "auto": hb.ALGO_AUTO}[algo]
+    rng = np.random.default_rng(count)
+    shards = [K.rnd(rng.standard_normal(count).astype(np.float32), dtype) for _ in range(R)]
+    bufs = on_all(worlds, lambda r, w: torch.from_numpy(shards[r]).to(f"cuda:{w.device()}", TORCH[dtype]))
+    # fp32 accumulation + one rounding stays within a rounding step of the reference's
+    # order of operations (each partial sum rounded, src/parallel/comm.rs:54-58)
+    ref = P.all_reduce(shards, dtype)
+    tol = {"f32": 1e-5, "f16": 4e-3, "bf16": 3e-2}[dtype]
+    assert np.max(np.abs(P.all_reduce_f32(shards, dtype) - ref)) <= tol * max(float(np.max(np.abs(ref))), 1.0)
+    for rep in range(2):  # the second call reuses the staging area
+        on_all(worlds, lambda r, w: w.all_reduce(bufs[r], code))
+        want = P.all_reduce_f32(shards, dtype)
+        for r in range(R):
+            assert np.array_equal(host(bufs[r]), want), (r, rep)
+        assert all(w.status() == 0 for w in worlds)
+        shards = [want.copy() for _ in range(R)]
+
+
+def test_all_reduce_reference_kats(hb, worlds, kats):
+    if len(worlds) < 2:
+        pytest.skip("two ranks")
+    case = kats["all_reduce"][1]
+    pad = 4  # 16-byte granularity of the peer path
+    vals = [np.array(s + [0.0] * (pad - len(s) % pad if len(s) % pad else 0), dtype=np.float32) for s in case["shards"]]
+    two = worlds[:2] if len(worlds) == 2 else None
+    if two is None:
+        pytest.skip("known-answer case is written for exactly two ranks")
+    bufs = on_all(two, lambda r, w: torch.from_numpy(vals[r]).to(f"cuda:{w.device()}"))
+    on_all(two, lambda r, w: w.all_reduce(bufs[r]))
+    for b in bufs:
+        assert host(b)[:4].tolist() == case["expect"]
+
+
+def test_all_reduce_errors(hb, worlds):
+    w = worlds[0]
+    with torch.cuda.device(w.device()):
+        buf = torch.zeros(8, device=f"cuda:{w.device()}")
+        with pytest.raises(hb.HbError) as ei:
+            hb.check(hb.lib.hb_all_reduce(w.handle, None, buf.data_ptr(), 0, hb.F32, 0))
+        assert "empty" in ei.value.msg
+        with pytest.raises(hb.HbError):
+            hb.check(hb.lib.hb_all_reduce(w.handle, None, buf.data_ptr(), 8, 7, 0))
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 8192, 8192), (8, 8192, 28672), (64, 8192, 8192), (128, 8192, 28672), (256, 4096, 4096)])
+@pytest.mark.parametrize("algo", ["auto", "one_shot", "two_shot"])
+def test_fused_rowparallel(hb, worlds, M, N, K_, algo):
+    """Config 3 of the baseline: X [M, K/TP] ~N(0,1), W [K/TP, N] ~N(0,0.02) per rank,
+    residual ~N(0,1), norm weight ones, eps 1e-5."""
+    R = len(worlds)
+    Kl = K_ // R
+    code = {"one_shot": hb.ALGO_ONE_SHOT, "two_shot": hb.ALGO_TWO_SHOT, "auto": hb.ALGO_AUTO}[algo]
+    xs = [K.round_bf16(np.random.default_rng(2 + r).standard_normal((M, Kl)).astype(np.float32)) for r in range(R)]
+    wt = [K.round_bf16((0.02 * np.random.default_rng(3 + r).standard_normal((N, Kl))).astype(np.float32)) for r in range(R)]
+    resid = K.round_bf16(np.random.default_rng(4).standard_normal((M, N)).astype(np.float32))
+    nw = np.ones(N, dtype=np.float32)
+
+    def put(a, w):
+        return torch.from_numpy(a).to(f"cuda:{w.device()}", torch.bfloat16)
+
+    ins = on_all(worlds, lambda r, w: (put(xs[r], w), put(wt[r], w), put(resid, w), put(nw, w)))
+    wss = on_all(worlds, lambda r, w: hb.fused_rowparallel_workspace(ins[r][0], ins[r][1]))
+    for rep in range(2):
+        outs = on_all(worlds, lambda r, w: hb.fused_rowparallel(w, *ins[r], 1e-5, code, workspace=wss[r]))
+        assert all(w.status() == 0 for w in worlds)
+        parts = [K.round_bf16((xs[r].astype(np.float64) @ wt[r].astype(np.float64).T).astype(np.float32)) for r in range(R)]
+        acc = resid.copy()
+        for p in parts:
+            acc = acc + p
+        want_h = K.round_bf16(acc)
+        want_n = K.rms_norm_kernel(want_h, nw, 1e-5, "bf16")
+        for r in range(R):
+            normed, res = outs[r]
+            scale = float(np.max(np.abs(want_h)))
+            assert float(np.max(np.abs(host(res) - want_h))) / scale <= 1e-2
+            assert float(np.max(np.abs(host(normed) - want_n))) / float(np.max(np.abs(want_n))) <= 2e-2
+            # every rank ends with the same bits
+            assert np.array_equal(host(res), host(outs[0][1])) and np.array_equal(host(normed), host(outs[0][0]))
+
+
+def test_tp_engine_matches_oracle(hb, worlds):
+    """A small bf16 model sharded over the ranks: logits of every rank against the
+    oracle with the same world size."""
+    from oracle import llama_ref as R_
+
+    R = len(worlds)
+    shape = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=16,
+                 num_key_value_heads=8, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+    engines = on_all(worlds, lambda r, w: hb.Engine.create_random(shape, seed=1, norm_ones=True, max_seq_len=64,
+                                                                   bf16=True, tensor_parallel_size=R, world=w, max_batch=8))
+    cfg = R_.LlamaTpConfig(**shape)
+    weights = {}
+    for name, shp in R_.tensor_shapes(cfg).items():
+        pieces = [engines[r].get_tensor(name) for r in range(R)]
+        if name.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "gate_proj.weight", "up_proj.weight")):
+            weights[name] = np.concatenate([p.reshape(shp[0] // R, shp[1]) for p in pieces], 0)
+        elif name.endswith(("o_proj.weight", "down_proj.weight")):
+            weights[name] = np.concatenate([p.reshape(shp[0], shp[1] // R) for p in pieces], 1)
+        else:
+            weights[name] = pieces[0].reshape(shp)
+    oracle = R_.LlamaTpOracle(cfg, weights, world_size=R, dtype="bf16", reference_reduce=False)
+    B, plen = 8, 6
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, plen)).astype(np.uint32)
+    seqs = on_all(worlds, lambda r, w: [engines[r].create_kv_cache() for _ in range(B)])
+    logits = [np.empty((B, cfg.vocab_size), dtype=np.float32) for _ in range(R)]
+    import threading
+
+    for t in range(plen):
+        # every rank's step blocks until its peers arrive: one host thread per rank
+        ths = [threading.Thread(target=lambda r=r: engines[r].decode_batch(seqs[r], prompts[:, t], logits=logits[r]))
+               for r in range(R)]
+        [th.start() for th in ths]
+        [th.join() for th in ths]
+    want = np.stack([oracle.forward(prompts[i].tolist(), 0, oracle.new_cache()) for i in range(B)])
+    for r in range(R):
+        err = float(np.max(np.abs(logits[r] - want))) / float(np.max(np.abs(want)))
+        assert err <= 2e-2, (r, err)
+        assert np.array_equal(logits[r], logits[0])
+    for e in engines:
+        e.close()

@@ -471,17 +471,7 @@ class TpWorld:
 
     def fused_rowparallel(self, x, w, resid, norm_w, eps: float, algo: int = ALGO_AUTO, stream=None):
         """(normed, new_resid) = fused o_proj/down_proj + all-reduce + residual + RMSNorm."""
-        import torch
-
-        M, Kl = x.shape
-        N = w.shape[0]
-        normed = torch.empty((M, N), dtype=x.dtype, device=x.device)
-        res = torch.empty((M, N), dtype=x.dtype, device=x.device)
-        ws_bytes = lib.hb_fused_rowparallel_workspace_bytes(M, N, Kl)
-        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
-        check(lib.hb_fused_rowparallel(self.handle, _stream(stream), _ptr(normed), _ptr(res), _ptr(x), _ptr(w),
-                                       _ptr(resid), _ptr(norm_w), M, N, Kl, float(eps), algo, _ptr(ws)))
-        return normed, res
+        return fused_rowparallel(self, x, w, resid, norm_w, eps, algo, stream)
 
     def close(self) -> None:
         if self.handle and self._owner:
@@ -493,6 +483,33 @@ class TpWorld:
             self.close()
         except Exception:
             pass
+
+
+def fused_rowparallel_workspace(x, w):
+    """A zeroed workspace for fused_rowparallel; may be kept and reused across calls."""
+    import torch
+
+    M, Kl = x.shape
+    n = lib.hb_fused_rowparallel_workspace_bytes(M, w.shape[0], Kl)
+    return torch.zeros(max(n, 16), dtype=torch.uint8, device=x.device)
+
+
+def fused_rowparallel(world, x, w, resid, norm_w, eps: float, algo: int = ALGO_AUTO, stream=None,
+                      workspace=None, out=None):
+    """(normed, new_resid) = rms_norm(resid + SUM_ranks x_r @ w_r.T) in one kernel per rank.
+    world is a TpWorld or None (single rank)."""
+    import torch
+
+    M, Kl = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = (torch.empty((M, N), dtype=x.dtype, device=x.device), torch.empty((M, N), dtype=x.dtype, device=x.device))
+    normed, res = out
+    ws = workspace if workspace is not None else fused_rowparallel_workspace(x, w)
+    check(lib.hb_fused_rowparallel(world.handle if world is not None else None, _stream(stream), _ptr(normed),
+                                   _ptr(res), _ptr(x), _ptr(w), _ptr(resid), _ptr(norm_w), M, N, Kl, float(eps),
+                                   algo, _ptr(ws)))
+    return normed, res
 
 
 # ---------------------------------------------------------------- scheduler mirror

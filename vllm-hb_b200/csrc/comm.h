@@ -11,14 +11,15 @@ namespace hb {
 
 constexpr int kMaxCommCtas = 128;
 constexpr size_t kFlagBytes = 64 * 1024;
+constexpr int kMaxFusedTiles = 256;  // N <= 32768 in the fused row-parallel kernel
 
 struct CommFlags {
   // written by peers (release, system scope), polled locally
   uint32_t done[HB_MAX_RANKS];                      // calls completed by rank p
   uint32_t arrive1[kMaxCommCtas][HB_MAX_RANKS];     // per-CTA: partials pushed
   uint32_t arrive2[kMaxCommCtas][HB_MAX_RANKS];     // per-CTA: reduced slice pushed
-  uint32_t tile_arrive[2048];                       // fused kernel: partial tiles received per owned tile
-  uint32_t gather_arrive[HB_MAX_RANKS];             // fused kernel: reduced tiles received from rank p
+  uint32_t pflag[kMaxFusedTiles * HB_MAX_RANKS];    // fused kernel: partial of tile t from rank p landed
+  uint32_t gflag[kMaxFusedTiles];                   // fused kernel: reduced tile t (+ row sums) landed
   // local only
   uint32_t seq;        // collectives completed on this rank
   uint32_t finished;   // CTAs of the running kernel that are done

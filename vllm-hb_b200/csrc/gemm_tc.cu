@@ -25,16 +25,9 @@
 
 #include "common.h"
 #include "gemm.h"
+#include "tc_core.cuh"
 
 namespace hb {
-
-constexpr int kTileN = 128;       // weight rows per CTA tile = UMMA M
-constexpr int kTileK = 64;        // bf16 elements per 128-byte swizzle row
-constexpr int kUmmaK = 16;
-constexpr int kMaxStages = 8;
-constexpr int kTcThreads = 128;
-constexpr uint32_t kSpinLimit = 1u << 21;
-constexpr size_t kCounterBlockBytes = 64 * 1024;  // int32 counters of up to 16384 tiles
 
 struct TcParams {
   int M, N;                 // N = weight rows (for SwiGLU: rows of gate == rows of up)
@@ -44,103 +37,12 @@ struct TcParams {
   int epilogue, out_f32;
   int64_t ldy;
   int up_row_offset;        // SwiGLU: first row of the up projection inside W
+  int packed;               // weights stored tile-major: [n_tile][k_chunk][128][64]
   void* Y;
   float* partials;
   int* counters;
   int* err_flag;
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000u)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false when the limit ran out or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 255u) == 255u && *s_abort) return false;
-  }
-  *s_abort = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 32 lanes x 16 consecutive fp32 columns: thread i gets lane (base_lane + i).
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 B,
-// groups of 8 rows (1024 B) repeat along the M/N dimension (stride byte offset 1024).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);        // start address, bits [0,14)
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                        // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;                        // layout type: 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, A and B K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(kTileN >> 4) << 24);
-}
-
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
 
 // ----------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -207,7 +109,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
         const int kx = (kc0 + i) * kTileK;
-        tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
+        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + i) * kTileN, full);
+        else tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
         if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
         tma_load_2d(sa + a_bytes * n_acc, &tm_x, kx, m_tile * p.m_pad, full);
         armed = i + 1;
@@ -310,16 +213,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const float* base = p.partials + unit * (int64_t)(n_acc * p.m_pad) * kTileN;
         const int64_t sstride = (int64_t)(n_acc * p.m_pad) * kTileN;
         const int m_lim = min(p.m_pad, p.M - m_base);
-        for (int m = 0; m < m_lim; ++m) {
-          float g = 0.f, u = 0.f;
+        // eight batch rows at a time: 8 (16 with SwiGLU) independent loads are in
+        // flight per split instead of one dependent chain per row
+        for (int m0 = 0; m0 < m_lim; m0 += 8) {
+          float g[8], u[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
           for (int s = 0; s < p.splits; ++s) {
-            g += __ldcg(base + s * sstride + (int64_t)m * kTileN + row);
-            if (swiglu) u += __ldcg(base + s * sstride + (int64_t)(p.m_pad + m) * kTileN + row);
+            const float* ps = base + s * sstride + row;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (m0 + j < m_lim) {
+                g[j] += __ldcg(ps + (int64_t)(m0 + j) * kTileN);
+                if (swiglu) u[j] += __ldcg(ps + (int64_t)(p.m_pad + m0 + j) * kTileN);
+              }
+            }
           }
-          if (swiglu) g = silu_f(g) * u;
-          if (n_glob < p.N) {
-            if (p.out_f32) ((float*)p.Y)[(int64_t)(m_base + m) * p.ldy + n_glob] = g;
-            else ((__nv_bfloat16*)p.Y)[(int64_t)(m_base + m) * p.ldy + n_glob] = __float2bfloat16_rn(g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int m = m0 + j;
+            if (m < m_lim && n_glob < p.N) {
+              const float r = swiglu ? silu_f(g[j]) * u[j] : g[j];
+              if (p.out_f32) ((float*)p.Y)[(int64_t)(m_base + m) * p.ldy + n_glob] = r;
+              else ((__nv_bfloat16*)p.Y)[(int64_t)(m_base + m) * p.ldy + n_glob] = __float2bfloat16_rn(r);
+            }
           }
         }
         if (tid == 0) p.counters[m_tile * p.n_tiles + tile] = 0;  // ready for the next launch
@@ -379,19 +296,13 @@ bool gemm_tc_supported(int64_t M, int64_t N, int64_t K, hb_dtype dtype) {
 }
 
 static int pick_splits(int units, int k_chunks, int slots) {
-  // choose the split factor with the least wave-quantisation loss; every split keeps
-  // at least four 64-wide K chunks so the pipeline fill is amortised
-  int best = 1;
-  double best_eff = 0.0;
-  const int max_s = std::max(1, std::min(16, k_chunks / 4));
-  for (int s = 1; s <= max_s; ++s) {
-    const double ctas = (double)units * s;
-    const double waves = std::ceil(ctas / slots);
-    double eff = ctas / (waves * slots);
-    eff -= 0.01 * (s - 1);  // prefer fewer splits when it is a wash
-    if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
-  }
-  return best;
+  // Measured on B200: a split through global scratch costs one fp32 accumulator tile
+  // (128 x m_pad x 4 B) written and read back per extra CTA, which outweighs the gain
+  // unless the K range per CTA is long and the batch small.  So: split in two only
+  // for few tiles with a deep K (the 8B down_proj: 32 tiles x 224 chunks, 94 -> 76 us).
+  (void)slots;
+  if (units * 4 <= 160 && k_chunks >= 128) return 2;
+  return 1;
 }
 
 int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
@@ -425,7 +336,8 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const size_t stage = (size_t)kTileN * kTileK * 2 * n_acc + (size_t)pl.m_pad * kTileK * 2;
   // two CTAs per SM when the stages allow it, so one CTA's epilogue hides under the
   // other's loads
-  const size_t budget = 110 * 1024;
+  size_t budget = 110 * 1024;
+  if (const char* ev = getenv("HB_TC_SMEM_KB")) budget = (size_t)atoi(ev) * 1024;  // experiment knob
   pl.stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, budget / stage));
   pl.smem_bytes = pl.stages * stage + 1024;
   if (pl.smem_bytes > di.smem_optin)
@@ -457,7 +369,8 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
       dev_done[cur] = true;
     }
   }
-  rc = encode_map(&pl.tm_w, W, N, K, kTileN);
+  if (getenv("HB_TC_PACKED")) rc = encode_map(&pl.tm_w, W, N * (K / kTileK), kTileK, kTileN);  // speed experiment
+  else rc = encode_map(&pl.tm_w, W, N, K, kTileN);
   if (rc) return rc;
   rc = encode_map(&pl.tm_x, X, M, K, pl.m_pad);
   return rc;
@@ -476,6 +389,7 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.epilogue = pl.epilogue; p.out_f32 = pl.out_f32 ? 1 : 0;
   p.ldy = ldy;
   p.up_row_offset = (int)pl.N;
+  p.packed = getenv("HB_TC_PACKED") ? 1 : 0;
   p.Y = Y;
   // counters first (16-byte aligned block), partials after
   p.counters = (int*)workspace;
