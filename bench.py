@@ -45,6 +45,10 @@ def workload_for(n_gpus: int, args) -> dict:
     if args.layers:
         w["shape"]["num_hidden_layers"] = args.layers
         w["name"] += f" layers{args.layers}"
+    if args.shape_scale > 1:  # debugging / CPU tests only: a proportionally smaller model
+        for k in ("hidden_size", "intermediate_size", "vocab_size"):
+            w["shape"][k] //= args.shape_scale
+        w["name"] += f" scaled-1/{args.shape_scale}"
     if args.batch:
         w["batch"] = args.batch
     if args.prompt_len:
@@ -321,6 +325,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
+    ap.add_argument("--shape-scale", type=int, default=1, help="shrink the model (debugging only)")
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--profile-steps", type=int, default=3)

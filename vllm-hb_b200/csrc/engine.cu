@@ -23,6 +23,7 @@
 #include "gemm.h"
 #include "json.h"
 #include "ops.h"
+#include "rowpar.h"
 #include "safetensors.h"
 
 struct hb_seq {
@@ -100,7 +101,8 @@ struct hb_engine {
   void* d_gemm_ws = nullptr;
   size_t gemm_ws_bytes = 0;
   int* d_err = nullptr;
-  bool use_tc = false, use_graph = true, fused_swiglu = true;
+  bool use_tc = false, use_graph = true, fused_swiglu = true, use_fused = false;
+  void* d_fused_ws = nullptr;
   std::map<int, hb::StepPlans> plans;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = -1.f;
@@ -300,6 +302,17 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
+  const char* uf = getenv("HB_UNFUSED");
+  e->use_fused = e->use_tc && !(uf && uf[0] == '1');
+  if (e->use_fused) {
+    const size_t fw = std::max(rowpar_fused_workspace_bytes(B, e->H, e->hq_l * e->hd),
+                               rowpar_fused_workspace_bytes(B, e->H, e->I_l));
+    if (fw == 0) e->use_fused = false;
+    else {
+      if ((rc = dev_alloc(e, &e->d_fused_ws, fw))) return rc;
+      HB_CUDA_CHECK(cudaMemset(e->d_fused_ws, 0, fw));
+    }
+  }
   return HB_OK;
 }
 
@@ -413,15 +426,22 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemm);
-    if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
-    if (e->ws > 1) {
-      prof_mark(e, kCatComm);
-      if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->hq_l * e->hd)) {
+      // one kernel: GEMM tiles -> peer staging -> reduce + residual -> row scales -> norm
+      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_attn, w.wo, e->d_h, w.norm_post, B, e->H,
+                             e->hq_l * e->hd, eps, HB_ALGO_AUTO, e->d_fused_ws))) return rc;
+      ++e->last_launches;
+    } else {
+      if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
+      if (e->ws > 1) {
+        prof_mark(e, kCatComm);
+        if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+        ++e->last_launches;
+      }
+      prof_mark(e, kCatNorm);
+      if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
       ++e->last_launches;
     }
-    prof_mark(e, kCatNorm);
-    if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
-    ++e->last_launches;
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
     prof_mark(e, kCatGemm);
     if (e->use_tc && e->fused_swiglu) {
@@ -432,18 +452,24 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_l, e->dtype))) return rc;
       ++e->last_launches;
     }
-    prof_mark(e, kCatGemm);
-    if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_l, false))) return rc;
-    if (e->ws > 1) {
-      prof_mark(e, kCatComm);
-      if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
-      ++e->last_launches;
-    }
     // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
     const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
-    prof_mark(e, kCatNorm);
-    if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, nw, B, e->H, eps, e->dtype))) return rc;
-    ++e->last_launches;
+    prof_mark(e, kCatGemm);
+    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->I_l)) {
+      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_l, eps,
+                             HB_ALGO_AUTO, e->d_fused_ws))) return rc;
+      ++e->last_launches;
+    } else {
+      if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_l, false))) return rc;
+      if (e->ws > 1) {
+        prof_mark(e, kCatComm);
+        if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+        ++e->last_launches;
+      }
+      prof_mark(e, kCatNorm);
+      if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, nw, B, e->H, eps, e->dtype))) return rc;
+      ++e->last_launches;
+    }
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
   prof_mark(e, kCatGemm);

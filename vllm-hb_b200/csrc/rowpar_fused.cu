@@ -402,9 +402,13 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 // ------------------------------------------------------------------------ host
 // Layout of the caller's workspace (zero-initialised once, left clean by every call):
 //   [0, 64K)          split-K tile counters
-//   [64K, 64K+P)      split-K fp32 partials
-//   single-rank only: [.., +64K) flag block, then the row-sum area — the memory that a
-//                     multi-rank world keeps in its staging buffer.
+//   [64K, 128K)       flag block   } single-rank only: the memory that a multi-rank
+//   [128K, 384K)      row sums     } world keeps in its staging buffer
+//   [384K, ...)       split-K fp32 partials
+// All offsets are fixed, so calls of different shapes may share one workspace.
+constexpr size_t kFusedRowsqBytes = (size_t)kMaxFusedTiles * 256 * sizeof(float);
+constexpr size_t kFusedPartialsOff = kCounterBlockBytes + kFlagBytes + kFusedRowsqBytes;
+
 struct FusedPlan {
   TcGemmPlan g;        // tensor maps and tile geometry (epilogue unused)
   int splits = 1;
@@ -438,10 +442,10 @@ static int fused_plan(FusedPlan* fp, const void* X, const void* W, int64_t M, in
   if ((rc = fused_capacity(device, fp->g.smem_bytes, &fp->capacity))) return rc;
   // tensor memory: two CTAs per SM at most share the 512 columns
   const int k_chunks = (int)(Kl / kTileK);
-  int s = std::max(1, fp->capacity / fp->g.n_tiles);
-  s = std::min(s, std::max(1, k_chunks / 2));
-  s = std::min(s, 16);
-  if (const char* ev = getenv("HB_FUSED_SPLITS")) s = std::max(1, std::min(atoi(ev), k_chunks));
+  // same rule as the plain GEMM: a split through global scratch pays off only for few
+  // tiles with a deep K
+  int s = (fp->g.n_tiles <= 40 && k_chunks >= 128) ? 2 : 1;
+  if (const char* ev = getenv("HB_FUSED_SPLITS")) s = std::max(1, std::min(std::min(atoi(ev), 4), k_chunks));
   while (s > 1 && fp->g.n_tiles * s > fp->capacity) --s;
   fp->splits = s;
   fp->partials_bytes = s > 1 ? (size_t)fp->g.n_tiles * s * fp->g.m_pad * kTileN * sizeof(float) : 0;
@@ -461,10 +465,8 @@ size_t rowpar_fused_workspace_bytes(int64_t M, int64_t N, int64_t K_local) {
   if (!rowpar_fused_supported(nullptr, M, N, K_local)) return 0;
   const size_t m_pad = (size_t)std::max<int64_t>(16, (M + 15) / 16 * 16);
   const size_t tiles = (size_t)(N / kTileN);
-  // bound on the partials for any split factor the plan may choose (<= 16)
-  size_t ws = kCounterBlockBytes + tiles * 16 * m_pad * kTileN * sizeof(float);
-  ws = align_up(ws, 256) + kFlagBytes + align_up(tiles * (size_t)M * sizeof(float), 256);
-  return ws + 256;
+  // bound on the partials for any split factor the plan may choose (<= 4)
+  return kFusedPartialsOff + tiles * 4 * m_pad * kTileN * sizeof(float) + 256;
 }
 
 int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* X,
@@ -493,7 +495,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   p.norm_w = (const __nv_bfloat16*)norm_w;
   uint8_t* wsb = (uint8_t*)workspace;
   p.counters = (int*)wsb;
-  p.partials = (float*)(wsb + kCounterBlockBytes);
+  p.partials = (float*)(wsb + kFusedPartialsOff);
   p.tile_bytes = (int64_t)M * kTileN * 2;
   bool two = false;
   if (R > 1) {
@@ -513,8 +515,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
     for (int q = 0; q < R; ++q) p.peer[q] = w->peer[q];
   } else {
     // single rank: flag block and row sums live in the caller's workspace
-    const size_t off = align_up(kCounterBlockBytes + fp.partials_bytes, 256);
-    p.peer[0] = wsb + off;
+    p.peer[0] = wsb + kCounterBlockBytes;
     p.gather_off = 0;
     p.rowsq_off = 0;
   }
