@@ -27,6 +27,7 @@ struct TcGemmPlan {
   int m_tiles = 0;    // ceil(M / m_pad)
   int n_tiles = 0;    // ceil(N / 128)
   int splits = 1;     // split-K factor
+  bool cluster = false;  // the splits of a tile form a thread-block cluster (on-chip reduction)
   int stages = 0;
   int tmem_cols = 0;
   size_t smem_bytes = 0;

@@ -38,6 +38,8 @@ struct TcParams {
   int64_t ldy;
   int up_row_offset;        // SwiGLU: first row of the up projection inside W
   int packed;               // weights stored tile-major: [n_tile][k_chunk][128][64]
+  int stagger;              // rotate the K walk per tile
+  int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
   void* Y;
   float* partials;
   int* counters;
@@ -62,7 +64,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   // work unit: blockIdx.x = tile * splits + split, blockIdx.y = batch tile
   const int tile = blockIdx.x / p.splits;
-  const int split = blockIdx.x % p.splits;
+  const int split = p.cluster ? (int)cluster_ctarank() : blockIdx.x % p.splits;
   const int m_tile = blockIdx.y;
   const int base_c = p.k_chunks / p.splits, rem_c = p.k_chunks % p.splits;
   const int kc0 = split * base_c + min(split, rem_c);
@@ -108,8 +110,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t full = smem_u32(&s_full[s]);
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
-        const int kx = (kc0 + i) * kTileK;
-        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + i) * kTileN, full);
+        // tiles walk their K range from different starting chunks so that the CTAs do
+        // not all ask L2 for the same slice of X at the same moment
+        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
+        const int kx = (kc0 + ci) * kTileK;
+        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + ci) * kTileN, full);
         else tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
         if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
         tma_load_2d(sa + a_bytes * n_acc, &tm_x, kx, m_tile * p.m_pad, full);
@@ -167,7 +172,72 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
   const bool ok_all = __syncthreads_and(have_acc ? 1 : 0) != 0;
 
-  if (ok_all) {
+  if (p.cluster && p.splits > 1) {
+    // ---- split-K inside a thread-block cluster: the partners exchange accumulator rows
+    // through distributed shared memory.  CTA r of the cluster owns the features
+    // [r*FW, (r+1)*FW) of the tile; everybody sends the rows it does not own to their
+    // owner, the owner adds the S partials in split order (deterministic) and runs the
+    // epilogue for its rows.  Both cluster barriers are reached unconditionally.
+    const int S = p.splits, FW = kTileN / S;
+    const int owner = row / FW, f_loc = row % FW;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][n_acc][m_pad][FW]
+    const int slot_floats = n_acc * p.m_pad * FW;
+    // tcgen05.ld is warp-collective: whole warps take the branches below, lanes are
+    // masked only at the stores
+    const int own_lo = (warp * 32) / FW, own_hi = (warp * 32 + 31) / FW;
+    const bool warp_sends = !(own_lo == split && own_hi == split);
+    const bool warp_owns = own_lo <= split && split <= own_hi;
+    cluster_sync_all();  // every partner's pipeline buffers are idle from here on
+    if (ok_all && warp_sends) {
+      const int slot = split < owner ? split : split - 1;
+      const uint32_t dst0 = cluster_map(smem_base + (uint32_t)(slot * slot_floats + f_loc) * 4u, (uint32_t)owner);
+      for (int acc = 0; acc < n_acc; ++acc) {
+        for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+          float v[16];
+          tmem_ld16(t_lane + acc * p.m_pad + c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (owner != split) st_cluster_f32(dst0 + (uint32_t)((acc * p.m_pad + c0 + j) * FW) * 4u, v[j]);
+        }
+      }
+    }
+    cluster_sync_all();  // release/acquire: the rows sent above are visible to their owner
+    if (ok_all && warp_owns) {
+      for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+        float own[16], own_u[16], g[16], u[16];
+        tmem_ld16(t_lane + c0, own);
+        if (swiglu) tmem_ld16(t_lane + p.m_pad + c0, own_u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+        for (int src = 0; src < S; ++src) {
+          if (src == split) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { g[j] += own[j]; if (swiglu) u[j] += own_u[j]; }
+          } else {
+            const float* rs = recv + (src < split ? src : src - 1) * slot_floats + f_loc;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              g[j] += rs[(c0 + j) * FW];
+              if (swiglu) u[j] += rs[(p.m_pad + c0 + j) * FW];
+            }
+          }
+        }
+        if (n_glob < p.N && owner == split) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m_base + c0 + j;
+            if (m < p.M) {
+              const float r = swiglu ? silu_f(g[j]) * u[j] : g[j];
+              if (p.out_f32) ((float*)p.Y)[(int64_t)m * p.ldy + n_glob] = r;
+              else ((__nv_bfloat16*)p.Y)[(int64_t)m * p.ldy + n_glob] = __float2bfloat16_rn(r);
+            }
+          }
+        }
+      }
+    }
+    if (!ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
+  } else if (ok_all) {
     if (p.splits == 1) {
       for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
         float v[16];
@@ -305,6 +375,16 @@ static int pick_splits(int units, int k_chunks, int slots) {
   return 1;
 }
 
+// Split factor when the partners reduce on chip (thread-block cluster + distributed
+// shared memory).  One SM draws at most ~34 GB/s of weights from HBM (measured), so
+// every GEMM wants at least one CTA on each SM: the smallest power of two that
+// covers the SMs, at most 8 (portable cluster size), each CTA keeping >= 4 K chunks.
+static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
+  int s = 1;
+  while (s < 8 && units * s < sm_count && k_chunks / (s * 2) >= 4) s *= 2;
+  return s;
+}
+
 int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
                  int epilogue, bool out_f32, int device, int force_splits) {
   if (!gemm_tc_supported(M, N, K, HB_BF16))
@@ -345,15 +425,29 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const int ctas_per_sm = std::max(1, std::min<int>((int)(di.smem_optin / pl.smem_bytes), 512 / pl.tmem_cols));
   const int k_chunks = (int)(K / kTileK);
   const int slots = di.sm_count * std::min(ctas_per_sm, 2);
-  pl.splits = force_splits > 0 ? std::min(force_splits, k_chunks)
-                               : pick_splits(pl.n_tiles * pl.m_tiles, k_chunks, slots);
+  const char* cl_env = getenv("HB_TC_CLUSTER");
+  const bool want_cluster = !(cl_env && cl_env[0] == '0');
+  if (force_splits > 0) pl.splits = std::min(force_splits, k_chunks);
+  else if (want_cluster) pl.splits = pick_cluster_splits(pl.n_tiles * pl.m_tiles, k_chunks, di.sm_count);
+  else pl.splits = pick_splits(pl.n_tiles * pl.m_tiles, k_chunks, slots);
+  // cluster form: power-of-two size <= 8 whose receive buffers fit the pipeline's
+  // shared memory; anything else reduces through global scratch
+  pl.cluster = false;
+  auto recv_fits = [&](int sp) {
+    return (size_t)(sp - 1) * n_acc * pl.m_pad * (kTileN / sp) * sizeof(float) <= (size_t)pl.stages * stage;
+  };
+  if (want_cluster && pl.splits > 1) {
+    if (force_splits <= 0)
+      while (pl.splits > 1 && !recv_fits(pl.splits)) pl.splits /= 2;
+    pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 && recv_fits(pl.splits);
+  }
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
   // partials where they expect zeroed counters.
-  if (units * sizeof(int) > kCounterBlockBytes) pl.splits = 1;
-  pl.ws_partials_bytes = pl.splits > 1 ? units * pl.splits * n_acc * pl.m_pad * kTileN * sizeof(float) : 0;
-  pl.ws_counters_bytes = pl.splits > 1 ? kCounterBlockBytes : 0;
+  if (!pl.cluster && units * sizeof(int) > kCounterBlockBytes) pl.splits = 1;
+  pl.ws_partials_bytes = (pl.splits > 1 && !pl.cluster) ? units * pl.splits * n_acc * pl.m_pad * kTileN * sizeof(float) : 0;
+  pl.ws_counters_bytes = (pl.splits > 1 && !pl.cluster) ? kCounterBlockBytes : 0;
   // opt in to the large dynamic shared memory window once per device (here, not at
   // launch, so that launches stay legal inside a stream capture)
   {
@@ -378,7 +472,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
 
 int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
                 int* err_flag) {
-  if (pl.splits > 1 && !workspace)
+  if (pl.splits > 1 && !pl.cluster && !workspace)
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: split-K plan needs a workspace of %zu bytes",
                 pl.workspace_bytes());
   TcParams p;
@@ -395,9 +489,28 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.counters = (int*)workspace;
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
+  p.cluster = pl.cluster ? 1 : 0;
+  { const char* sg = getenv("HB_TC_STAGGER"); p.stagger = (sg && sg[0] == '1') ? 1 : 0; }  // measured: no gain, off
   dim3 grid((unsigned)(pl.n_tiles * pl.splits), (unsigned)pl.m_tiles);
-  gemm_tc_kernel<<<grid, kTcThreads, pl.smem_bytes, st>>>(pl.tm_w, pl.tm_x, p);
-  HB_LAUNCH_CHECK();
+  if (pl.cluster) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)pl.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, pl.tm_w, pl.tm_x, p));
+  } else {
+    gemm_tc_kernel<<<grid, kTcThreads, pl.smem_bytes, st>>>(pl.tm_w, pl.tm_x, p);
+    HB_LAUNCH_CHECK();
+  }
   return HB_OK;
 }
 
