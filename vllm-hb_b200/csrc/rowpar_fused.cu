@@ -7,27 +7,29 @@
 // loop (src/engine/arch/llama_tp.rs:327,533-552 and :339,563-571,517-522), which the
 // reference runs as a library GEMM, an NCCL all-reduce, peer copies and a norm kernel.
 //
-// Phases of a CTA = (128-feature tile t, K split s):
+// Phases of a CTA = (128-feature tile t, K split s); the S splits of a tile form a
+// thread-block cluster:
 //   1. tcgen05 mainloop (TMA -> shared memory -> UMMA, fp32 accumulator in tensor
 //      memory), exactly the decode GEMM: the weight slab is the UMMA A operand.
-//   2. split-K: partials meet in local scratch; the last CTA of a tile goes on as the
-//      tile's "finisher", the others exit.
-//   3. the finisher rounds the rank's partial tile to bf16 (the reference's partials are
-//      bf16 tensors), stages it in shared memory and PUSHES it with coalesced 128-bit
-//      stores into the staging buffer of the tile's reducer rank(s) over NVLink, then
-//      raises pflag[t][me] there.  two-shot: the reducer of tile t is rank t/(T/R);
-//      one-shot: every rank reduces every tile (one NVLink hop, R-1 times the bytes).
-//   4. a reducer waits for the R-1 remote partials of its tile, sums all R in rank
+//   2. split-K on chip: CTA s owns the 128/S features [s*FW, (s+1)*FW) of the tile — the
+//      "unit" t*S+s; partners send it their accumulator rows through distributed shared
+//      memory and it adds the S partials in split order.
+//   3. every CTA rounds its unit of the rank's partial to bf16 (the reference's partials
+//      are bf16 tensors), keeps it in shared memory and PUSHES it with coalesced 128-bit
+//      stores into the staging buffer of the unit's reducer rank(s) over NVLink, then
+//      raises pflag[u][me] there.  two-shot: the reducer of unit u is rank u/(U/R);
+//      one-shot: every rank reduces every unit (one NVLink hop, R-1 times the bytes).
+//   4. a reducer waits for the R-1 remote partials of its unit, sums all R in rank
 //      order in fp32 on top of the residual, rounds, writes resid_out, accumulates the
-//      per-row sum of squares of the rounded tile, and (two-shot) pushes the reduced
-//      tile and the row sums to every peer, then raises gflag[t] everywhere.
-//   5. every finisher waits until all T tiles (hence all row sums) are present locally,
-//      computes the row scales and writes its tile of normed_out (non-reducers also copy
-//      the gathered tile into resid_out).
+//      per-row sum of squares of the rounded unit, and (two-shot) pushes the reduced
+//      unit and the row sums to every peer, then raises gflag[u] everywhere.
+//   5. every CTA waits until all U units (hence all row sums) are present locally,
+//      computes the row scales and writes its unit of normed_out (non-reducers also copy
+//      the gathered unit into resid_out).
 // Flags carry the device-resident call sequence number, so a captured CUDA graph can
 // replay the kernel; staging reuse is guarded by the per-rank "done" flags shared with
-// the all-reduce kernel.  The grid is launched cooperatively (all CTAs co-resident)
-// because finishers wait for other CTAs of the same grid.  All waits are bounded.
+// the all-reduce kernel.  CTAs wait for other CTAs of the same grid, so the grid never
+// exceeds the number of CTAs the device can hold at once.  All waits are bounded.
 #include <algorithm>
 #include <mutex>
 
@@ -96,14 +98,13 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __shared__ __align__(8) uint64_t s_done;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
-  __shared__ int s_last;
   __shared__ uint32_t s_seq;
   __shared__ float s_rowsq[256];
   __shared__ float s_rs[256];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x / p.splits;
-  const int split = blockIdx.x % p.splits;
+  const int split = p.splits > 1 ? (int)cluster_ctarank() : 0;
   const int base_c = p.k_chunks / p.splits, rem_c = p.k_chunks % p.splits;
   const int kc0 = split * base_c + min(split, rem_c);
   const int n_kc = base_c + (split < rem_c ? 1 : 0);
@@ -121,7 +122,6 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
     mbar_init(smem_u32(&s_done), 1);
     s_abort = 0;
-    s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -189,205 +189,206 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   const bool have_acc = mbar_wait(smem_u32(&s_done), 0, &s_abort);
   tc_fence_after();
-  const int row = warp * 32 + lane;  // accumulator row = feature inside the tile
+  const int row = warp * 32 + lane;  // accumulator row = feature inside the 128-wide tile
   const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-  bool ok_all = __syncthreads_and(have_acc ? 1 : 0) != 0;
-  bool finisher = ok_all;
+  const bool ok_all = __syncthreads_and(have_acc ? 1 : 0) != 0;
 
-  // ------------------------------------------------------------ 2. split-K
-  if (ok_all && p.splits > 1) {
-    float* mine = p.partials + ((int64_t)tile * p.splits + split) * (int64_t)p.m_pad * kTileN;
-    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
-      float v[16];
-      tmem_ld16(t_lane + c0, v);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) mine[(int64_t)(c0 + j) * kTileN + row] = v[j];
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int prev = atomicAdd(&p.counters[tile], 1);
-      s_last = (prev == p.splits - 1);
-      if (s_last) p.counters[tile] = 0;
-    }
-    __syncthreads();
-    finisher = s_last != 0;
-    if (finisher) __threadfence();
-  }
-
-  CommFlags* fl = reinterpret_cast<CommFlags*>(p.peer[p.rank]);
-  bool proto_ok = true;
-
-  if (finisher) {
-    const int R = p.ws, me = p.rank, T = p.n_tiles;
-    __nv_bfloat16* tile_s = reinterpret_cast<__nv_bfloat16*>(smem_gen);  // [M][128] bf16
-    uint4* tile_u4 = reinterpret_cast<uint4*>(smem_gen);
-    const int n_u4 = p.M * 16;  // 16-byte vectors in the tile
-
-    // ---- 3a. this rank's partial tile, rounded to bf16, into shared memory
-    if (p.splits == 1) {
+  // ------------------------------------------------------------ 2. split-K in the cluster
+  // CTA r of the cluster owns features [r*FW, (r+1)*FW) of the tile = "unit" tile*S + r.
+  // Partners send the accumulator rows they do not own to the owner through distributed
+  // shared memory; the owner adds the S partials in split order, rounds to bf16 (the
+  // reference's partials are bf16 tensors) and leaves its unit [M][FW] in shared memory.
+  const int S = p.splits, FW = kTileN / S;
+  const int owner = row / FW, f_loc = row % FW;
+  float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][m_pad][FW] fp32
+  const int slot_floats = p.m_pad * FW;
+  const uint32_t recv_bytes = (uint32_t)((S - 1) * slot_floats * 4);
+  __nv_bfloat16* tile_s = reinterpret_cast<__nv_bfloat16*>(smem_gen + recv_bytes);  // [M][FW] bf16
+  uint4* tile_u4 = reinterpret_cast<uint4*>(smem_gen + recv_bytes);
+  const int own_lo = (warp * 32) / FW, own_hi = (warp * 32 + 31) / FW;
+  const bool warp_sends = !(own_lo == split && own_hi == split);
+  const bool warp_owns = own_lo <= split && split <= own_hi;
+  if (S > 1) {
+    cluster_sync_all();  // every partner's pipeline buffers are idle from here on
+    if (ok_all && warp_sends) {
+      const int slot = split < owner ? split : split - 1;
+      const uint32_t dst0 = cluster_map(smem_base + (uint32_t)(slot * slot_floats + f_loc) * 4u, (uint32_t)owner);
       for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
         float v[16];
-        tmem_ld16(t_lane + c0, v);
+        tmem_ld16(t_lane + c0, v);  // warp-collective: lanes are masked at the store only
 #pragma unroll
         for (int j = 0; j < 16; ++j)
-          if (c0 + j < p.M) tile_s[(c0 + j) * kTileN + row] = __float2bfloat16_rn(v[j]);
-      }
-    } else {
-      const float* base = p.partials + (int64_t)tile * p.splits * (int64_t)p.m_pad * kTileN + row;
-      const int64_t sstride = (int64_t)p.m_pad * kTileN;
-      for (int m0 = 0; m0 < p.M; m0 += 8) {
-        float g[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (m0 + j < p.M) g[j] += __ldcg(base + s * sstride + (int64_t)(m0 + j) * kTileN);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (m0 + j < p.M) tile_s[(m0 + j) * kTileN + row] = __float2bfloat16_rn(g[j]);
+          if (owner != split) st_cluster_f32(dst0 + (uint32_t)((c0 + j) * FW) * 4u, v[j]);
       }
     }
-    if (tid == 0) s_seq = *reinterpret_cast<volatile uint32_t*>(&fl->seq);
-    __syncthreads();
-    const uint32_t seq = s_seq, target = seq + 1;
+    cluster_sync_all();  // release/acquire: rows sent above are visible to their owner
+  }
+  if (ok_all && warp_owns) {
+    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+      float own[16], g[16];
+      tmem_ld16(t_lane + c0, own);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) g[j] = 0.f;
+      for (int src = 0; src < S; ++src) {
+        if (src == split) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] += own[j];
+        } else {
+          const float* rs = recv + (src < split ? src : src - 1) * slot_floats + f_loc;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] += rs[(c0 + j) * FW];
+        }
+      }
+      if (owner == split) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < p.M) tile_s[(c0 + j) * FW + f_loc] = __float2bfloat16_rn(g[j]);
+      }
+    }
+  }
+  __syncthreads();
 
-    const int owner = p.two_shot ? tile / p.tiles_own : me;
-    const bool reducer = !p.two_shot || owner == me;
-    const int t_slot = p.two_shot ? tile - owner * p.tiles_own : tile;
-    auto data_of = [&](int q) { return (uint8_t*)p.peer[q] + kFlagBytes; };
-    auto flags_of = [&](int q) { return reinterpret_cast<CommFlags*>(p.peer[q]); };
-    auto part_slot = [&](int q, int src, int slot) {
-      return reinterpret_cast<uint4*>(data_of(q) + ((int64_t)src * p.tiles_own + slot) * p.tile_bytes);
-    };
+  // ------------------------------------------------------------ 3..5 unit protocol
+  CommFlags* fl = reinterpret_cast<CommFlags*>(p.peer[p.rank]);
+  bool proto_ok = ok_all;
+  const int R = p.ws, me = p.rank;
+  const int unit = tile * S + split, U = p.n_tiles * S;
+  const int lpr = FW / 8;            // 16-byte vectors (lanes) per batch row of the unit
+  const int n_u4 = p.M * lpr;
+  const int n0 = tile * kTileN + split * FW;  // first feature of the unit
+  if (tid == 0) s_seq = *reinterpret_cast<volatile uint32_t*>(&fl->seq);
+  __syncthreads();
+  const uint32_t seq = s_seq, target = seq + 1;
+  const int owner_rank = p.two_shot ? unit / p.tiles_own : me;
+  const bool reducer = !p.two_shot || owner_rank == me;
+  const int u_slot = p.two_shot ? unit - owner_rank * p.tiles_own : unit;
+  auto data_of = [&](int q) { return (uint8_t*)p.peer[q] + kFlagBytes; };
+  auto flags_of = [&](int q) { return reinterpret_cast<CommFlags*>(p.peer[q]); };
+  auto part_slot = [&](int q, int src, int slot) {
+    return reinterpret_cast<uint4*>(data_of(q) + ((int64_t)src * p.tiles_own + slot) * p.tile_bytes);
+  };
 
+  if (R > 1) {
+    // ---- A. peers must be done with the previous collective before their staging is written
+    bool ok = true;
+    if (tid < R && tid != me) ok = f_wait_ge(&fl->done[tid], seq);
+    proto_ok = __syncthreads_and((ok && proto_ok) ? 1 : 0) != 0;
+    // ---- 3. push this rank's partial of the unit to its reducer(s), coalesced 128-bit stores
+    if (proto_ok) {
+      for (int q = 0; q < R; ++q) {
+        if (q == me || (p.two_shot && q != owner_rank)) continue;
+        uint4* dst = part_slot(q, me, u_slot);
+        for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid < R && tid != me && (!p.two_shot || tid == owner_rank))
+        f_st_release(&flags_of(tid)->pflag[unit * HB_MAX_RANKS + me], target);
+    }
+  }
+
+  // ---- 4. reduce over ranks (rank order, fp32) on top of the residual
+  if (proto_ok && reducer) {
     if (R > 1) {
-      // ---- A. peers must be done with the previous collective before their staging is written
       bool ok = true;
-      if (tid < R && tid != me) ok = f_wait_ge(&fl->done[tid], seq);
-      proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
-      // ---- 3b. push the partial to the reducer(s)
-      if (proto_ok) {
-        for (int q = 0; q < R; ++q) {
-          if (q == me || (p.two_shot && q != owner)) continue;
-          uint4* dst = part_slot(q, me, t_slot);
-          for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (tid < R && tid != me && (!p.two_shot || tid == owner))
-          f_st_release(&flags_of(tid)->pflag[tile * HB_MAX_RANKS + me], target);
-      }
-    }
-
-    // ---- 4. reduce
-    if (proto_ok && reducer) {
-      if (R > 1) {
-        bool ok = true;
-        if (tid < R && tid != me) ok = f_wait_ge(&fl->pflag[tile * HB_MAX_RANKS + tid], target);
-        proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
-      }
-      if (proto_ok) {
-        for (int i0 = 0; i0 < n_u4; i0 += kTcThreads) {
-          const int i = i0 + tid;
-          float ss = 0.f;
-          if (i < n_u4) {
-            const int m = i >> 4, c = i & 15;
-            const int64_t g_off = (int64_t)m * p.N + tile * kTileN + c * 8;
-            float acc[8], t8[8];
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.resid_in + g_off), acc);
-            for (int src = 0; src < R; ++src) {
-              const uint4 raw = (src == me) ? tile_u4[i] : __ldcg(part_slot(me, src, t_slot) + i);
-              bf16x8_to_f32(raw, t8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] += t8[j];
-            }
-            const uint4 out = f32_to_bf16x8(acc);
-            bf16x8_to_f32(out, t8);  // the norm sees the rounded residual
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ss += t8[j] * t8[j];
-            tile_u4[i] = out;
-            *reinterpret_cast<uint4*>(p.resid_out + g_off) = out;
-          }
-          // 16 consecutive lanes hold one batch row of the tile
-#pragma unroll
-          for (int o = 8; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          if (i < n_u4 && (i & 15) == 0) s_rowsq[i >> 4] = ss;
-        }
-        __syncthreads();
-        float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + (int64_t)tile * p.M;
-        for (int m = tid; m < p.M; m += kTcThreads) my_rowsq[m] = s_rowsq[m];
-        if (R > 1 && p.two_shot) {
-          for (int q = 0; q < R; ++q) {
-            if (q == me) continue;
-            uint4* dst = reinterpret_cast<uint4*>(data_of(q) + p.gather_off + (int64_t)tile * p.tile_bytes);
-            for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
-            float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + (int64_t)tile * p.M;
-            for (int m = tid; m < p.M; m += kTcThreads) rq[m] = s_rowsq[m];
-          }
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (tid == 0) f_st_release(&fl->gflag[tile], target);
-        if (R > 1 && p.two_shot && tid < R && tid != me) f_st_release(&flags_of(tid)->gflag[tile], target);
-      }
-    }
-
-    // ---- 5. all tiles present -> row scales -> normalise this tile
-    if (proto_ok) {
-      bool ok = true;
-      for (int t2 = tid; t2 < T; t2 += kTcThreads) ok = ok && f_wait_ge(&fl->gflag[t2], target);
+      if (tid < R && tid != me) ok = f_wait_ge(&fl->pflag[unit * HB_MAX_RANKS + tid], target);
       proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
     if (proto_ok) {
-      const float* rowsq = reinterpret_cast<const float*>(data_of(me) + p.rowsq_off);
-      for (int m = tid; m < p.M; m += kTcThreads) {
-        float s = 0.f;
-        for (int t2 = 0; t2 < T; ++t2) s += __ldcg(rowsq + (int64_t)t2 * p.M + m);
-        s_rs[m] = rsqrtf(s / (float)p.N + p.eps);
-      }
-      if (!reducer) {
-        const uint4* src = reinterpret_cast<const uint4*>(data_of(me) + p.gather_off + (int64_t)tile * p.tile_bytes);
-        for (int i = tid; i < n_u4; i += kTcThreads) {
-          const uint4 v = __ldcg(src + i);
-          tile_u4[i] = v;
-          const int m = i >> 4, c = i & 15;
-          *reinterpret_cast<uint4*>(p.resid_out + (int64_t)m * p.N + tile * kTileN + c * 8) = v;
+      for (int i0 = 0; i0 < n_u4; i0 += kTcThreads) {
+        const int i = i0 + tid;
+        float ss = 0.f;
+        if (i < n_u4) {
+          const int m = i / lpr, c = i % lpr;
+          const int64_t g_off = (int64_t)m * p.N + n0 + c * 8;
+          float acc[8], t8[8];
+          bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.resid_in + g_off), acc);
+          for (int src = 0; src < R; ++src) {
+            const uint4 raw = (src == me) ? tile_u4[i] : __ldcg(part_slot(me, src, u_slot) + i);
+            bf16x8_to_f32(raw, t8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += t8[j];
+          }
+          const uint4 out = f32_to_bf16x8(acc);
+          bf16x8_to_f32(out, t8);  // the norm sees the rounded residual
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += t8[j] * t8[j];
+          tile_u4[i] = out;
+          *reinterpret_cast<uint4*>(p.resid_out + g_off) = out;
         }
+        // lpr consecutive lanes hold one batch row of the unit (lpr is 2, 4, 8 or 16)
+        for (int o = lpr >> 1; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (i < n_u4 && (i % lpr) == 0) s_rowsq[i / lpr] = ss;
       }
       __syncthreads();
-      if (p.normed_out) {
-        for (int i = tid; i < n_u4; i += kTcThreads) {
-          const int m = i >> 4, c = i & 15;
-          float h[8], w8[8];
-          bf16x8_to_f32(tile_u4[i], h);
-          bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.norm_w + tile * kTileN + c * 8), w8);
-          const float r = s_rs[m];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) h[j] = h[j] * r * w8[j];
-          *reinterpret_cast<uint4*>(p.normed_out + (int64_t)m * p.N + tile * kTileN + c * 8) = f32_to_bf16x8(h);
+      float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + (int64_t)unit * p.M;
+      for (int m = tid; m < p.M; m += kTcThreads) my_rowsq[m] = s_rowsq[m];
+      if (R > 1 && p.two_shot) {
+        for (int q = 0; q < R; ++q) {
+          if (q == me) continue;
+          uint4* dst = reinterpret_cast<uint4*>(data_of(q) + p.gather_off + (int64_t)unit * p.tile_bytes);
+          for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
+          float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + (int64_t)unit * p.M;
+          for (int m = tid; m < p.M; m += kTcThreads) rq[m] = s_rowsq[m];
         }
       }
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0) f_st_release(&fl->gflag[unit], target);
+      if (R > 1 && p.two_shot && tid < R && tid != me) f_st_release(&flags_of(tid)->gflag[unit], target);
     }
+  }
 
-    // ---- E. the last finisher closes the collective
-    __syncthreads();
-    if (tid == 0) {
-      if (!proto_ok) atomicExch(&fl->status, HB_ERR_TIMEOUT);
-      __threadfence();
-      const uint32_t prev = atomicAdd(&fl->finished, 1u);
-      if (prev == (uint32_t)T - 1) {
-        fl->finished = 0;
-        *reinterpret_cast<volatile uint32_t*>(&fl->seq) = target;
-        __threadfence_system();
-        for (int q = 0; q < R; ++q)
-          if (q != me) f_st_release(&flags_of(q)->done[me], target);
+  // ---- 5. all units present -> row scales -> normalise this unit
+  if (proto_ok) {
+    bool ok = true;
+    for (int u2 = tid; u2 < U; u2 += kTcThreads) ok = ok && f_wait_ge(&fl->gflag[u2], target);
+    proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  }
+  if (proto_ok) {
+    const float* rowsq = reinterpret_cast<const float*>(data_of(me) + p.rowsq_off);
+    for (int m = tid; m < p.M; m += kTcThreads) {
+      float s = 0.f;
+      for (int u2 = 0; u2 < U; ++u2) s += __ldcg(rowsq + (int64_t)u2 * p.M + m);
+      s_rs[m] = rsqrtf(s / (float)p.N + p.eps);
+    }
+    if (!reducer) {
+      const uint4* src = reinterpret_cast<const uint4*>(data_of(me) + p.gather_off + (int64_t)unit * p.tile_bytes);
+      for (int i = tid; i < n_u4; i += kTcThreads) {
+        const uint4 v = __ldcg(src + i);
+        tile_u4[i] = v;
+        const int m = i / lpr, c = i % lpr;
+        *reinterpret_cast<uint4*>(p.resid_out + (int64_t)m * p.N + n0 + c * 8) = v;
       }
     }
-  } else if (!ok_all && tid == 0) {
-    atomicExch(&fl->status, HB_ERR_TIMEOUT);
+    __syncthreads();
+    if (p.normed_out) {
+      for (int i = tid; i < n_u4; i += kTcThreads) {
+        const int m = i / lpr, c = i % lpr;
+        float h[8], w8[8];
+        bf16x8_to_f32(tile_u4[i], h);
+        bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.norm_w + n0 + c * 8), w8);
+        const float r = s_rs[m];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = h[j] * r * w8[j];
+        *reinterpret_cast<uint4*>(p.normed_out + (int64_t)m * p.N + n0 + c * 8) = f32_to_bf16x8(h);
+      }
+    }
+  }
+
+  // ---- E. the last CTA closes the collective
+  __syncthreads();
+  if (tid == 0) {
+    if (!proto_ok) atomicExch(&fl->status, HB_ERR_TIMEOUT);
+    __threadfence();
+    const uint32_t prev = atomicAdd(&fl->finished, 1u);
+    if (prev == (uint32_t)U - 1) {
+      fl->finished = 0;
+      *reinterpret_cast<volatile uint32_t*>(&fl->seq) = target;
+      __threadfence_system();
+      for (int q = 0; q < R; ++q)
+        if (q != me) f_st_release(&flags_of(q)->done[me], target);
+    }
   }
 
   tc_fence_before();
@@ -399,21 +400,19 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
 }
 
+
 // ------------------------------------------------------------------------ host
-// Layout of the caller's workspace (zero-initialised once, left clean by every call):
-//   [0, 64K)          split-K tile counters
-//   [64K, 128K)       flag block   } single-rank only: the memory that a multi-rank
-//   [128K, 384K)      row sums     } world keeps in its staging buffer
-//   [384K, ...)       split-K fp32 partials
+// Layout of the caller's workspace (zero-initialised once, left clean by every call);
+// only a single-rank call uses it, for what a multi-rank world keeps in its staging:
+//   [0, 64K)      flag block
+//   [64K, 320K)   row sums [unit][M]
 // All offsets are fixed, so calls of different shapes may share one workspace.
 constexpr size_t kFusedRowsqBytes = (size_t)kMaxFusedTiles * 256 * sizeof(float);
-constexpr size_t kFusedPartialsOff = kCounterBlockBytes + kFlagBytes + kFusedRowsqBytes;
 
 struct FusedPlan {
   TcGemmPlan g;        // tensor maps and tile geometry (epilogue unused)
-  int splits = 1;
+  int splits = 1;      // cluster size S: power of two, <= 8
   int capacity = 0;    // co-resident CTAs of the kernel on this device
-  size_t partials_bytes = 0;
 };
 
 static int fused_capacity(int device, size_t smem_bytes, int* out) {
@@ -439,16 +438,31 @@ static int fused_plan(FusedPlan* fp, const void* X, const void* W, int64_t M, in
                       int device) {
   int rc = gemm_tc_plan(&fp->g, X, W, M, N, Kl, kEpiStore, false, device, 1);
   if (rc) return rc;
+  fp->g.splits = 1;
+  fp->g.cluster = false;
   if ((rc = fused_capacity(device, fp->g.smem_bytes, &fp->capacity))) return rc;
-  // tensor memory: two CTAs per SM at most share the 512 columns
+  DeviceInfo di;
+  if ((rc = device_info(device, &di))) return rc;
   const int k_chunks = (int)(Kl / kTileK);
-  // same rule as the plain GEMM: a split through global scratch pays off only for few
-  // tiles with a deep K
-  int s = (fp->g.n_tiles <= 40 && k_chunks >= 128) ? 2 : 1;
-  if (const char* ev = getenv("HB_FUSED_SPLITS")) s = std::max(1, std::min(std::min(atoi(ev), 4), k_chunks));
-  while (s > 1 && fp->g.n_tiles * s > fp->capacity) --s;
+  const int T = fp->g.n_tiles;
+  const size_t pipe_bytes = fp->g.smem_bytes - 1024;
+  auto fits = [&](int s) {
+    const size_t fw = kTileN / s;
+    const size_t recv = (size_t)(s - 1) * fp->g.m_pad * fw * sizeof(float);
+    const size_t unit = (size_t)M * fw * 2;
+    // units are capped by the flag arrays; a cluster leaves a little slack in the
+    // co-residency bound because its CTAs must land in one GPC
+    return recv + unit <= pipe_bytes && T * s <= kMaxFusedTiles && T * s <= fp->capacity - (s > 1 ? 8 : 0);
+  };
+  // at least one CTA per SM when possible (one SM draws ~34 GB/s from HBM at most)
+  int s = 1;
+  while (s < 8 && T * s < di.sm_count && k_chunks / (s * 2) >= 4 && fits(s * 2)) s *= 2;
+  if (const char* ev = getenv("HB_FUSED_SPLITS")) {
+    const int want = atoi(ev);
+    if ((want == 1 || want == 2 || want == 4 || want == 8) && want <= k_chunks && fits(want)) s = want;
+  }
+  if (!fits(s)) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: %d tiles do not fit the device", T);
   fp->splits = s;
-  fp->partials_bytes = s > 1 ? (size_t)fp->g.n_tiles * s * fp->g.m_pad * kTileN * sizeof(float) : 0;
   return HB_OK;
 }
 
@@ -463,10 +477,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 size_t rowpar_fused_workspace_bytes(int64_t M, int64_t N, int64_t K_local) {
   if (!rowpar_fused_supported(nullptr, M, N, K_local)) return 0;
-  const size_t m_pad = (size_t)std::max<int64_t>(16, (M + 15) / 16 * 16);
-  const size_t tiles = (size_t)(N / kTileN);
-  // bound on the partials for any split factor the plan may choose (<= 4)
-  return kFusedPartialsOff + tiles * 4 * m_pad * kTileN * sizeof(float) + 256;
+  return kFlagBytes + kFusedRowsqBytes + 256;
 }
 
 int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* X,
@@ -482,10 +493,10 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   int rc = fused_plan(&fp, X, W, M, N, K_local, device);
   if (rc) return rc;
   const int R = w ? w->ws : 1;
-  const int T = fp.g.n_tiles;
+  const int T = fp.g.n_tiles, S = fp.splits, U = T * S, FW = kTileN / S;
   FusedParams p;
   memset(&p, 0, sizeof(p));
-  p.M = (int)M; p.N = (int)N; p.m_pad = fp.g.m_pad; p.splits = fp.splits; p.stages = fp.g.stages;
+  p.M = (int)M; p.N = (int)N; p.m_pad = fp.g.m_pad; p.splits = S; p.stages = fp.g.stages;
   p.tmem_cols = fp.g.tmem_cols; p.k_chunks = (int)(K_local / kTileK); p.n_tiles = T;
   p.ws = R; p.rank = w ? w->rank : 0;
   p.eps = eps;
@@ -494,20 +505,18 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   p.normed_out = (__nv_bfloat16*)normed_out;
   p.norm_w = (const __nv_bfloat16*)norm_w;
   uint8_t* wsb = (uint8_t*)workspace;
-  p.counters = (int*)wsb;
-  p.partials = (float*)(wsb + kFusedPartialsOff);
-  p.tile_bytes = (int64_t)M * kTileN * 2;
+  p.tile_bytes = (int64_t)M * FW * 2;  // one unit: [M][FW] bf16
   bool two = false;
   if (R > 1) {
     two = algo == HB_ALGO_TWO_SHOT || (algo == HB_ALGO_AUTO && R > 2 && (size_t)M * N * 2 >= 256 * 1024);
-    if (T % R != 0) two = false;
+    if (U % R != 0) two = false;
   }
   p.two_shot = two ? 1 : 0;
-  p.tiles_own = two ? T / R : T;
+  p.tiles_own = two ? U / R : U;  // units a reducer rank owns
   const size_t part_area = (size_t)R * p.tiles_own * p.tile_bytes;
   p.gather_off = (int64_t)align_up(part_area, 256);
-  p.rowsq_off = p.gather_off + (int64_t)align_up(two ? (size_t)T * p.tile_bytes : 0, 256);
-  const size_t need = (size_t)p.rowsq_off + (size_t)T * M * sizeof(float);
+  p.rowsq_off = p.gather_off + (int64_t)align_up(two ? (size_t)U * p.tile_bytes : 0, 256);
+  const size_t need = (size_t)p.rowsq_off + (size_t)U * M * sizeof(float);
   if (R > 1) {
     if (need > w->staging_bytes)
       return fail(HB_ERR_INVALID_ARG, "fused row-parallel: needs %zu bytes of staging, world has %zu", need,
@@ -515,24 +524,35 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
     for (int q = 0; q < R; ++q) p.peer[q] = w->peer[q];
   } else {
     // single rank: flag block and row sums live in the caller's workspace
-    p.peer[0] = wsb + kCounterBlockBytes;
+    p.peer[0] = wsb;
     p.gather_off = 0;
     p.rowsq_off = 0;
   }
-  if (T * fp.splits > fp.capacity)
-    return fail(HB_ERR_INVALID_ARG, "fused row-parallel: %d tiles do not fit the %d co-resident CTAs", T,
-                fp.capacity);
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)(T * fp.splits));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)U);
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = fp.g.smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
+  if (S > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+  } else {
+    attr[0].id = cudaLaunchAttributeCooperative;  // co-residency checked by the driver
+    attr[0].val.cooperative = 1;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (S > 1) {
+    // CTAs of this grid wait for one another: every cluster must be resident at once
+    int max_clusters = 0;
+    HB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&max_clusters, rowpar_fused_kernel, &cfg));
+    if (U / S > max_clusters)
+      return fail(HB_ERR_INVALID_ARG, "fused row-parallel: %d clusters of %d CTAs, device holds %d at once",
+                  U / S, S, max_clusters);
+  }
   HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, rowpar_fused_kernel, fp.g.tm_w, fp.g.tm_x, p));
   return HB_OK;
 }
