@@ -127,6 +127,27 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
                               int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
                               int64_t num_blocks, int n_splits, void* workspace, hb_dtype dtype);
 
+/* The same split-KV decode attention for callers that must not allocate device memory
+ * — a host that runs inside a captured or pre-planned memory budget, an embedding
+ * runtime whose allocator the library may not touch, an interrupt-like serving loop
+ * that forbids cudaMalloc after start-up.  (No counterpart in the reference: its
+ * attention is a doc-only stub and every one of its kernels allocates its output.)
+ * The split partials go to an 8 MiB array built into the library image, resident on
+ * every GPU that loads the library until the process ends; a request whose partials
+ * (hb_attention_workspace_bytes) exceed hb_paged_decode_attention_static_max_bytes()
+ * is refused with HB_ERR_INVALID_ARG.  Nothing in the array has to start at zero
+ * (every partial is written before it is read), but all calls share it: two calls
+ * that overlap on the GPU — different streams, or the same arguments from two
+ * threads — race on it.  The first call on each device looks the array's address
+ * up; make that first call outside any stream capture.  No cudaMalloc/cudaFree or
+ * other allocating routine is called. */
+size_t hb_paged_decode_attention_static_max_bytes(void);
+int hb_paged_decode_attention_static(void* stream, void* out, const void* q, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables,
+                                     const int32_t* ctx_lens, int64_t n_seqs, int n_q_heads,
+                                     int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
+                                     int64_t num_blocks, int n_splits, hb_dtype dtype);
+
 /* Y[M,N] = X[M,K] . W[N,K]^T  (weights stored [out,in] and applied as x.W^T, as every
  * matmul of the path does: src/engine/arch/llama_tp.rs:232-234,327,335-337,354).
  * bf16 with K%64==0 and N%8==0 runs on tcgen05 tensor cores (swap-AB: the weight's

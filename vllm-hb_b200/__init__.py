@@ -93,6 +93,8 @@ _SIGS = {
     "hb_kv_assign_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i]),
     "hb_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "hb_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _vp, _i]),
+    "hb_paged_decode_attention_static_max_bytes": (_sz, []),
+    "hb_paged_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _i]),
     "hb_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
     "hb_gemm": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
     "hb_gemm_ex_workspace_bytes": (_sz, [_i64, _i64, _i64, _i, _i]),
@@ -309,6 +311,20 @@ def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, n_splits
                                         _ptr(block_tables), _ptr(ctx_lens), n_seqs, hq, hkv, d,
                                         block_tables.shape[1], num_blocks, n_splits, _ptr(ws),
                                         dtype_code(q.dtype)))
+    return out
+
+
+def paged_decode_attention_static(q, k_cache, v_cache, block_tables, ctx_lens, n_splits: int = 2, stream=None):
+    """paged_decode_attention without any allocation by the library: the split partials
+    use the array built into libhb.so (bounded size; calls must not overlap on the GPU)."""
+    import torch
+
+    n_seqs, hq, d = q.shape
+    num_blocks, hkv = k_cache.shape[0], k_cache.shape[1]
+    out = torch.empty_like(q)
+    check(lib.hb_paged_decode_attention_static(_stream(stream), _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                               _ptr(block_tables), _ptr(ctx_lens), n_seqs, hq, hkv, d,
+                                               block_tables.shape[1], num_blocks, n_splits, dtype_code(q.dtype)))
     return out
 
 

@@ -12,6 +12,7 @@
 //
 // Pool layout per layer: [num_blocks, n_kv_heads, 16, head_dim].
 #include <cfloat>
+#include <mutex>
 
 #include "common.h"
 
@@ -352,6 +353,71 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads,
                              head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------
+// Split-KV decode attention for callers that cannot allocate device memory.
+//
+// The split partials (unnormalised outputs and the (max, sum) pairs) live in a
+// file-scope device array instead of a caller-provided workspace.  Every GPU that
+// loads this library carries the array until the process exits.
+namespace hb {
+
+constexpr size_t kStaticAttnScratchBytes = 8u << 20;  // 8 MiB per device
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticAttnScratchBytes];
+
+// In host code `g_attn_static_scratch` is only a handle for the runtime, not a device
+// address: the address is asked for once per device, with that device current.
+static int static_attn_scratch(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  HB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(HB_ERR_INVALID_ARG, "device %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    HB_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_attn_static_scratch));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return HB_OK;
+}
+
+}  // namespace hb
+
+extern "C" {
+
+size_t hb_paged_decode_attention_static_max_bytes(void) { return hb::kStaticAttnScratchBytes; }
+
+int hb_paged_decode_attention_static(void* stream, void* out, const void* q, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables,
+                                     const int32_t* ctx_lens, int64_t n_seqs, int n_q_heads,
+                                     int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
+                                     int64_t num_blocks, int n_splits, hb_dtype dtype) {
+  HB_CHECK_ARG(out && q && k_cache && v_cache && block_tables && ctx_lens,
+               "hb_paged_decode_attention_static: null pointer");
+  HB_CHECK_ARG(n_seqs >= 0 && n_seqs <= 65535, "hb_paged_decode_attention_static: n_seqs %lld out of range",
+               (long long)n_seqs);
+  HB_CHECK_ARG(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0,
+               "hb_paged_decode_attention_static: n_q_heads must be a multiple of n_kv_heads");
+  HB_CHECK_ARG(n_splits >= 1 && n_splits <= 64, "hb_paged_decode_attention_static: n_splits out of range");
+  HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention_static: bad block counts");
+  const size_t need = hb_attention_workspace_bytes(n_seqs, n_q_heads, head_dim, n_splits);
+  if (need > hb::kStaticAttnScratchBytes)
+    return hb::fail(HB_ERR_INVALID_ARG,
+                    "hb_paged_decode_attention_static: %lld sequences x %d heads x %d splits need %zu bytes of "
+                    "split scratch, the built-in array holds %zu; use fewer splits or "
+                    "hb_paged_decode_attention with a workspace of your own",
+                    (long long)n_seqs, n_q_heads, n_splits, need, hb::kStaticAttnScratchBytes);
+  void* scratch = nullptr;
+  int rc = hb::static_attn_scratch(&scratch);
+  if (rc) return rc;
+  return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache, v_cache,
+                             block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
+                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype);
 }
 
 }  // extern "C"
