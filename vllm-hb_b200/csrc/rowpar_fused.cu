@@ -253,6 +253,7 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   bool proto_ok = ok_all;
   const int R = p.ws, me = p.rank;
   const int unit = tile * S + split, U = p.n_tiles * S;
+  const int u_stride = (U + 3) & ~3;  // row stride of the [m][unit] row-sum table
   const int lpr = FW / 8;            // 16-byte vectors (lanes) per batch row of the unit
   const int n_u4 = p.M * lpr;
   const int n0 = tile * kTileN + split * FW;  // first feature of the unit
@@ -321,15 +322,17 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (i < n_u4 && (i % lpr) == 0) s_rowsq[i / lpr] = ss;
       }
       __syncthreads();
-      float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + (int64_t)unit * p.M;
-      for (int m = tid; m < p.M; m += kTcThreads) my_rowsq[m] = s_rowsq[m];
+      // row sums are kept [m][unit] (unit fastest) so that a reader sums a batch row with
+      // 128-bit loads
+      float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + unit;
+      for (int m = tid; m < p.M; m += kTcThreads) my_rowsq[(int64_t)m * u_stride] = s_rowsq[m];
       if (R > 1 && p.two_shot) {
         for (int q = 0; q < R; ++q) {
           if (q == me) continue;
           uint4* dst = reinterpret_cast<uint4*>(data_of(q) + p.gather_off + (int64_t)unit * p.tile_bytes);
           for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
-          float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + (int64_t)unit * p.M;
-          for (int m = tid; m < p.M; m += kTcThreads) rq[m] = s_rowsq[m];
+          float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + unit;
+          for (int m = tid; m < p.M; m += kTcThreads) rq[(int64_t)m * u_stride] = s_rowsq[m];
         }
       }
       __threadfence_system();
@@ -346,11 +349,34 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
   if (proto_ok) {
+    // sum of squares of every batch row over all units: tpr threads per row, each with
+    // eight independent 128-bit loads in flight, partials combined in a fixed order
     const float* rowsq = reinterpret_cast<const float*>(data_of(me) + p.rowsq_off);
-    for (int m = tid; m < p.M; m += kTcThreads) {
-      float s = 0.f;
-      for (int u2 = 0; u2 < U; ++u2) s += __ldcg(rowsq + (int64_t)u2 * p.M + m);
-      s_rs[m] = rsqrtf(s / (float)p.N + p.eps);
+    const int tpr = p.M >= kTcThreads ? 1 : (kTcThreads / p.M >= 4 ? 4 : (kTcThreads / p.M >= 2 ? 2 : 1));
+    const int u4_total = U >> 2;
+    for (int m0 = 0; m0 < p.M; m0 += kTcThreads / tpr) {
+      const int m = m0 + tid / tpr, part = tid % tpr;
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+      if (m < p.M) {
+        const float4* r4 = reinterpret_cast<const float4*>(rowsq + (int64_t)m * u_stride);
+        for (int i = part * 8; i < u4_total; i += tpr * 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (i + j < u4_total) {
+              const float4 v = __ldcg(r4 + i + j);
+              a[j] += (v.x + v.y) + (v.z + v.w);
+            }
+          }
+        }
+        if (part == 0)
+          for (int u2 = u4_total << 2; u2 < U; ++u2) a[0] += __ldcg(rowsq + (int64_t)m * u_stride + u2);
+      }
+      float s = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+      // tpr is 1, 2 or 4 and divides the warp: combine the partials of a row
+      for (int o = tpr >> 1; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (m < p.M && part == 0) s_rs[m] = rsqrtf(s / (float)p.N + p.eps);
     }
     if (!reducer) {
       const uint4* src = reinterpret_cast<const uint4*>(data_of(me) + p.gather_off + (int64_t)unit * p.tile_bytes);
@@ -516,7 +542,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   const size_t part_area = (size_t)R * p.tiles_own * p.tile_bytes;
   p.gather_off = (int64_t)align_up(part_area, 256);
   p.rowsq_off = p.gather_off + (int64_t)align_up(two ? (size_t)U * p.tile_bytes : 0, 256);
-  const size_t need = (size_t)p.rowsq_off + (size_t)U * M * sizeof(float);
+  const size_t need = (size_t)p.rowsq_off + (size_t)((U + 3) & ~3) * M * sizeof(float);
   if (R > 1) {
     if (need > w->staging_bytes)
       return fail(HB_ERR_INVALID_ARG, "fused row-parallel: needs %zu bytes of staging, world has %zu", need,
