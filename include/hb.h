@@ -376,9 +376,11 @@ int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t*
                     uint32_t* next_tokens, float* logits_opt);
 /* One decode step issued kernel by kernel (no graph) with CUDA events between the
  * kernels: ms_by_kind receives HB_PROFILE_KINDS floats = device time spent in
- * 0 GEMMs, 1 decode attention, 2 RoPE + KV write, 3 (add +) RMSNorm, 4 embedding /
- * argmax / SwiGLU gate, 5 all-reduce.  The step counts like any other decode step. */
-#define HB_PROFILE_KINDS 6
+ * 0 QKV projection, 1 decode attention, 2 RoPE + KV write, 3 (add +) RMSNorm, 4 embedding /
+ * argmax / SwiGLU gate, 5 all-reduce, 6 o_proj, 7 gate|up projection, 8 down_proj,
+ * 9 lm_head (6 and 8 include the fused all-reduce + residual + norm when that kernel
+ * runs).  The step counts like any other decode step. */
+#define HB_PROFILE_KINDS 10
 int hb_engine_profile_step(hb_engine* e, hb_seq* const* seqs, size_t B,
                            const uint32_t* last_tokens, uint32_t* next_tokens, float* ms_by_kind);
 /* Algorithmic bytes all GEMM launches of one decode step move for batch B on this rank

@@ -709,7 +709,8 @@ class Engine:
                                   logits.ctypes.data if logits is not None else None))
         return next_tokens
 
-    PROFILE_KINDS = ("gemm", "attention", "rope_kv", "norm", "other", "all_reduce")
+    PROFILE_KINDS = ("gemm_qkv", "attention", "rope_kv", "norm", "other", "all_reduce",
+                     "gemm_o_proj", "gemm_gate_up", "gemm_down", "gemm_lm_head")
 
     def profile_step(self, seqs: Sequence[Sequence_], last_tokens: np.ndarray) -> tuple[np.ndarray, dict]:
         """One eager decode step with per-kernel-kind device times (ms)."""
@@ -719,7 +720,9 @@ class Engine:
         nxt = np.empty(B, dtype=np.uint32)
         ms = np.zeros(len(self.PROFILE_KINDS), dtype=np.float32)
         check(lib.hb_engine_profile_step(self.handle, arr, B, last.ctypes.data, nxt.ctypes.data, ms.ctypes.data))
-        return nxt, dict(zip(self.PROFILE_KINDS, ms.tolist()))
+        by_kind = dict(zip(self.PROFILE_KINDS, ms.tolist()))
+        by_kind["gemm"] = sum(v for k, v in by_kind.items() if k.startswith("gemm_"))
+        return nxt, by_kind
 
     def gemm_bytes(self, batch: int) -> float:
         return lib.hb_engine_gemm_bytes(self.handle, batch)

@@ -53,6 +53,7 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
                   const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens,
                   int hq, int hkv, int64_t max_blocks, int64_t num_blocks, int n_splits,
                   float scale, int64_t q_stride) {
+  pdl_trigger();
   constexpr int N = Vec16<T>::N;       // elements per 16-byte vector
   constexpr int LPR = HD / N;          // lanes covering one row
   constexpr int RPP = 32 / LPR;        // rows per warp pass
@@ -249,6 +250,7 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
 template <typename T>
 __global__ void attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                   const float* __restrict__ part_ml, int n_splits, int hd) {
+  pdl_trigger();
   const int64_t head = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(head * n_splits + s) * 2]);

@@ -112,7 +112,7 @@ all_reduce_kernel(const ArParams p) {
         }
       }
     }
-    __threadfence_system();
+    // bar.sync + the flag threads' system-scope release store publish every thread's stores
     __syncthreads();
     if (tid < R && tid != me) st_release_sys(&peer_flags(tid)->arrive1[b][me], target);
     ok = true;
@@ -146,7 +146,6 @@ all_reduce_kernel(const ArParams p) {
       }
     }
     if (p.two_shot) {
-      __threadfence_system();
       __syncthreads();
       if (tid < R && tid != me) st_release_sys(&peer_flags(tid)->arrive2[b][me], target);
       ok = true;

@@ -76,6 +76,11 @@ template <typename T> struct Vec16 {
   }
 };
 
+// Programmatic dependent launch: lets a successor that was launched with the
+// programmatic-serialisation attribute begin its prologue (it still waits for this
+// grid to finish before it reads what this grid writes).  A no-op otherwise.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -112,7 +112,7 @@ struct hb_engine {
   std::vector<cudaEvent_t> prof_events;
   std::vector<int> prof_cats;
   size_t prof_used = 0;
-  float prof_ms[8] = {0};
+  float prof_ms[16] = {0};
 };
 
 namespace hb {
@@ -302,8 +302,12 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
+  // A single rank has nothing to reduce: GEMM followed by add+norm is the faster
+  // sequence there (measured).  HB_UNFUSED=1 / HB_FUSED=1 force either path.
   const char* uf = getenv("HB_UNFUSED");
-  e->use_fused = e->use_tc && !(uf && uf[0] == '1');
+  const char* ff = getenv("HB_FUSED");
+  e->use_fused = e->use_tc && e->ws > 1 && !(uf && uf[0] == '1');
+  if (e->use_tc && ff && ff[0] == '1') e->use_fused = true;
   if (e->use_fused) {
     const size_t fw = std::max(rowpar_fused_workspace_bytes(B, e->H, e->hq_l * e->hd),
                                rowpar_fused_workspace_bytes(B, e->H, e->I_l));
@@ -376,7 +380,9 @@ static int run_gemm(hb_engine* e, StepPlans* sp, int64_t l, int kind, void* Y, c
   return gemm_simt(e->stream, Y, X, W, B, N, K, e->dtype, out_f32);
 }
 
-enum ProfCat { kCatGemm = 0, kCatAttention = 1, kCatRopeKv = 2, kCatNorm = 3, kCatOther = 4, kCatComm = 5, kNumCats = 6 };
+// kCatGemm is the QKV projection; the other projections have kinds of their own
+enum ProfCat { kCatGemm = 0, kCatAttention = 1, kCatRopeKv = 2, kCatNorm = 3, kCatOther = 4, kCatComm = 5,
+               kCatGemmO = 6, kCatGemmGateUp = 7, kCatGemmDown = 8, kCatGemmLmHead = 9, kNumCats = 10 };
 
 // While profiling, every call opens a timed segment of kind `cat` on the stream.
 static void prof_mark(hb_engine* e, int cat) {
@@ -425,7 +431,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
                               e->dtype))) return rc;
     e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
-    prof_mark(e, kCatGemm);
+    prof_mark(e, kCatGemmO);
     if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->hq_l * e->hd)) {
       // one kernel: GEMM tiles -> peer staging -> reduce + residual -> row scales -> norm
       if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_attn, w.wo, e->d_h, w.norm_post, B, e->H,
@@ -443,7 +449,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       ++e->last_launches;
     }
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
-    prof_mark(e, kCatGemm);
+    prof_mark(e, kCatGemmGateUp);
     if (e->use_tc && e->fused_swiglu) {
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
     } else {
@@ -454,7 +460,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     }
     // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
     const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
-    prof_mark(e, kCatGemm);
+    prof_mark(e, kCatGemmDown);
     if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->I_l)) {
       if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_l, eps,
                              HB_ALGO_AUTO, e->d_fused_ws))) return rc;
@@ -472,7 +478,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     }
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
-  prof_mark(e, kCatGemm);
+  prof_mark(e, kCatGemmLmHead);
   if ((rc = run_gemm(e, sp, 0, kLmHead, e->d_logits, e->d_x, e->lm_head, B, e->V, e->H, true))) return rc;
   prof_mark(e, kCatOther);
   if ((rc = hb_argmax(st, e->d_next, e->d_logits, B, e->V, HB_F32))) return rc;

@@ -33,6 +33,7 @@ struct TcGemmPlan {
   size_t smem_bytes = 0;
   int epilogue = kEpiStore;
   bool out_f32 = false;
+  bool tma_store = false;  // output rows are 16-byte multiples: bulk tensor stores
   // scratch layout inside the caller's workspace
   size_t ws_partials_bytes = 0;  // fp32 [m_tiles*n_tiles*splits][m_pad][128]
   size_t ws_counters_bytes = 0;  // int32 [m_tiles*n_tiles] (zero between calls)

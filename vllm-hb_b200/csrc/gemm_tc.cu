@@ -40,16 +40,42 @@ struct TcParams {
   int packed;               // weights stored tile-major: [n_tile][k_chunk][128][64]
   int stagger;              // rotate the K walk per tile
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
+  int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
   void* Y;
   float* partials;
   int* counters;
   int* err_flag;
 };
 
+// Optional phase timestamps (compiled in with -DHB_TC_TRACE only): every CTA records
+// the global timer at eight points of its life into a device array that
+// hb_debug_tc_trace() copies out.
+#ifdef HB_TC_TRACE
+constexpr int kTraceCtas = 4096, kTraceSlots = 16;
+static __device__ unsigned long long g_tc_trace[kTraceCtas * kTraceSlots];
+__device__ __forceinline__ void tc_trace(int slot) {
+  const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+  if (cta >= kTraceCtas) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  g_tc_trace[cta * kTraceSlots + slot] = t;
+  if (slot == 0) {
+    unsigned sm;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+    g_tc_trace[cta * kTraceSlots + 9] = sm;
+    g_tc_trace[cta * kTraceSlots + 8] = (unsigned long long)clock64();
+  }
+  if (slot == 7) g_tc_trace[cta * kTraceSlots + 15] = (unsigned long long)clock64();
+}
+#define TC_TRACE(cond, slot) do { if (cond) tc_trace(slot); } while (0)
+#else
+#define TC_TRACE(cond, slot) do { } while (0)
+#endif
+
 // ----------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-               const TcParams p) {
+               const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
@@ -61,6 +87,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool swiglu = p.epilogue == kEpiSwiGLU;
   const int n_acc = swiglu ? 2 : 1;
+  TC_TRACE(tid == 0, 0);
 
   // work unit: blockIdx.x = tile * splits + split, blockIdx.y = batch tile
   const int tile = blockIdx.x / p.splits;
@@ -98,20 +125,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
+  TC_TRACE(tid == 0, 1);
+  pdl_launch_dependents();  // the next kernel may start its own prologue / weight prefetch
+  if (!(warp == 0 && lane == 0)) pdl_wait();  // the producer waits after its weight prefetch
 
   if (warp == 0) {
     if (lane == 0) {
       // ---------------------------------------------------------- TMA producer
       int armed = 0;  // k-chunks whose copies were issued
-      for (int i = 0; i < n_kc; ++i) {
+      // Weights never depend on the previous kernel: the first stages' weight slabs are
+      // requested before waiting for it; activations only afterwards.
+      const int pre = min(p.stages, n_kc);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t full = smem_u32(&s_full[i]);
+        const uint32_t sa = smem_base + i * stage_bytes;
+        mbar_expect_tx(full, stage_bytes);
+        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
+        const int kx = (kc0 + ci) * kTileK;
+        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + ci) * kTileN, full);
+        else tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
+        if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
+        tma_load_2d(smem_base + i * stage_bytes + a_bytes * n_acc, &tm_x, (kc0 + ci) * kTileK, m_tile * p.m_pad,
+                    smem_u32(&s_full[i]));
+      }
+      armed = pre;
+      for (int i = pre; i < n_kc; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-        if (i >= p.stages && !mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, &s_abort)) break;
+        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, &s_abort)) break;
         const uint32_t full = smem_u32(&s_full[s]);
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
-        // tiles walk their K range from different starting chunks so that the CTAs do
-        // not all ask L2 for the same slice of X at the same moment
         const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
         const int kx = (kc0 + ci) * kTileK;
         if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + ci) * kTileN, full);
@@ -141,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
         ok = mbar_wait(smem_u32(&s_full[s]), ph, &s_abort);
         if (!ok) break;
+        TC_TRACE(i == 0, 2);
         tc_fence_after();
         const uint32_t sa = smem_base + s * stage_bytes;
         const uint64_t b_desc = make_smem_desc(sa + a_bytes * n_acc);
@@ -158,85 +207,168 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
         tc_commit(smem_u32(&s_empty[s]));  // frees the stage once these MMAs have read it
       }
-      if (ok) tc_commit(smem_u32(&s_done));
+      // only this thread polls for the accumulator; the other 127 sleep at the CTA
+      // barrier below (a polling warp occupies the SM's memory pipe, which slows the
+      // epilogue of a co-resident CTA several-fold)
+      if (ok) {
+        tc_commit(smem_u32(&s_done));
+        ok = mbar_wait(smem_u32(&s_done), 0, &s_abort);
+      }
+      if (!ok) s_abort = 1;
+      TC_TRACE(true, 3);
     }
     __syncwarp();
   }
 
   // ---------------------------------------------------------------- epilogue
-  const bool have_acc = mbar_wait(smem_u32(&s_done), 0, &s_abort);
-  tc_fence_after();
   const int row = warp * 32 + lane;              // accumulator row = output feature
   const int n_glob = tile * kTileN + row;
   const int m_base = m_tile * p.m_pad;
   const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const bool ok_all = __syncthreads_and(have_acc ? 1 : 0) != 0;
+  __syncthreads();
+  tc_fence_after();
+  const bool ok_all = s_abort == 0;
+  TC_TRACE(tid == 0, 4);
+
+  // Output tiles are staged in the (now idle) pipeline buffers as [batch row][128
+  // features] and leave through bulk tensor stores: one instruction per box instead of
+  // a 2- or 4-byte store per element (measured: 16 scalar store instructions per warp
+  // cost 1-2 us at the end of every GEMM).
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   if (p.cluster && p.splits > 1) {
-    // ---- split-K inside a thread-block cluster: the partners exchange accumulator rows
-    // through distributed shared memory.  CTA r of the cluster owns the features
-    // [r*FW, (r+1)*FW) of the tile; everybody sends the rows it does not own to their
-    // owner, the owner adds the S partials in split order (deterministic) and runs the
-    // epilogue for its rows.  Both cluster barriers are reached unconditionally.
-    const int S = p.splits, FW = kTileN / S;
-    const int owner = row / FW, f_loc = row % FW;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][n_acc][m_pad][FW]
-    const int slot_floats = n_acc * p.m_pad * FW;
-    // tcgen05.ld is warp-collective: whole warps take the branches below, lanes are
-    // masked only at the stores
-    const int own_lo = (warp * 32) / FW, own_hi = (warp * 32 + 31) / FW;
-    const bool warp_sends = !(own_lo == split && own_hi == split);
-    const bool warp_owns = own_lo <= split && split <= own_hi;
+    // ---- split-K inside a thread-block cluster: the partners exchange accumulator
+    // columns through distributed shared memory.  CTA r of the cluster owns the batch
+    // rows (accumulator columns) [r*CW, (r+1)*CW) of the tile for all 128 features;
+    // everybody sends the columns it does not own to their owner, the owner adds the S
+    // partials in split order (deterministic) and runs the epilogue for its rows.
+    // Both cluster barriers are reached unconditionally.
+    const int S = p.splits, CW = p.m_pad / S;          // CW is a multiple of 4
+    float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][n_acc][CW/4][128 features][4 columns]
+    const int slot_floats = n_acc * CW * kTileN;
+    const uint32_t out_off = (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
     cluster_sync_all();  // every partner's pipeline buffers are idle from here on
-    if (ok_all && warp_sends) {
-      const int slot = split < owner ? split : split - 1;
-      const uint32_t dst0 = cluster_map(smem_base + (uint32_t)(slot * slot_floats + f_loc) * 4u, (uint32_t)owner);
+    TC_TRACE(tid == 0, 5);
+    if (ok_all) {
       for (int acc = 0; acc < n_acc; ++acc) {
         for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+          // groups this CTA owns entirely stay in tensor memory (uniform over the CTA)
+          if (c0 / CW == split && (c0 + 15) / CW == split) continue;
           float v[16];
           tmem_ld16(t_lane + acc * p.m_pad + c0, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (owner != split) st_cluster_f32(dst0 + (uint32_t)((acc * p.m_pad + c0 + j) * FW) * 4u, v[j]);
+          for (int q = 0; q < 4; ++q) {
+            // four columns at a time: 16-byte remote stores, a warp fills 512 contiguous bytes
+            const int c = c0 + 4 * q, owner = c / CW;
+            if (owner != split) {
+              const int slot = split < owner ? split : split - 1;
+              const uint32_t local =
+                  smem_base +
+                  (uint32_t)(slot * slot_floats + ((acc * (CW >> 2) + ((c % CW) >> 2)) * kTileN + row) * 4) * 4u;
+              st_cluster_v4(cluster_map(local, (uint32_t)owner), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+          }
         }
       }
     }
-    cluster_sync_all();  // release/acquire: the rows sent above are visible to their owner
-    if (ok_all && warp_owns) {
-      for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+    cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
+    TC_TRACE(tid == 0, 6);
+    if (ok_all) {
+      const int c_lo = split * CW;
+      for (int c0 = c_lo & ~15; c0 < c_lo + CW; c0 += 16) {
         float own[16], own_u[16], g[16], u[16];
         tmem_ld16(t_lane + c0, own);
         if (swiglu) tmem_ld16(t_lane + p.m_pad + c0, own_u);
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+        // partials are added in split order (deterministic); the 16 columns are
+        // independent chains, so the loads and the activation overlap
         for (int src = 0; src < S; ++src) {
           if (src == split) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { g[j] += own[j]; if (swiglu) u[j] += own_u[j]; }
-          } else {
-            const float* rs = recv + (src < split ? src : src - 1) * slot_floats + f_loc;
-#pragma unroll
             for (int j = 0; j < 16; ++j) {
-              g[j] += rs[(c0 + j) * FW];
-              if (swiglu) u[j] += rs[(p.m_pad + c0 + j) * FW];
+              g[j] += own[j];
+              if (swiglu) u[j] += own_u[j];
+            }
+          } else {
+            const float* rs = recv + (src < split ? src : src - 1) * slot_floats;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int cl = c0 + 4 * q - c_lo;
+              if (cl >= 0 && cl < CW) {
+                const float4 t = *reinterpret_cast<const float4*>(rs + ((cl >> 2) * kTileN + row) * 4);
+                g[4 * q] += t.x; g[4 * q + 1] += t.y; g[4 * q + 2] += t.z; g[4 * q + 3] += t.w;
+                if (swiglu) {
+                  const float4 t2 =
+                      *reinterpret_cast<const float4*>(rs + (((CW >> 2) + (cl >> 2)) * kTileN + row) * 4);
+                  u[4 * q] += t2.x; u[4 * q + 1] += t2.y; u[4 * q + 2] += t2.z; u[4 * q + 3] += t2.w;
+                }
+              }
             }
           }
         }
-        if (n_glob < p.N && owner == split) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m_base + c0 + j;
-            if (m < p.M) {
-              const float r = swiglu ? silu_f(g[j]) * u[j] : g[j];
-              if (p.out_f32) ((float*)p.Y)[(int64_t)m * p.ldy + n_glob] = r;
-              else ((__nv_bfloat16*)p.Y)[(int64_t)m * p.ldy + n_glob] = __float2bfloat16_rn(r);
-            }
+        for (int j = 0; j < 16; ++j) g[j] = swiglu ? silu_f(g[j]) * u[j] : g[j];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int cl = c0 + j - c_lo;
+          if (cl >= 0 && cl < CW) {
+            if (p.out_f32) reinterpret_cast<float*>(smem_gen + out_off)[cl * kTileN + row] = g[j];
+            else reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off)[cl * kTileN + row] = __float2bfloat16_rn(g[j]);
           }
         }
       }
+      fence_async_smem();
     }
+    TC_TRACE(tid == 0, 10);
+    __syncthreads();
+    TC_TRACE(tid == 0, 11);
+    if (ok_all && tid == 0 && m_base + split * CW < p.M) {
+      tma_store_2d(&tm_y, smem_base + out_off, tile * kTileN, m_base + split * CW);
+      tma_store_commit();
+      tma_store_wait_read();
+    }
+    TC_TRACE(tid == 0, 12);
     if (!ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
+  } else if (ok_all && p.splits == 1 && p.tma_store) {
+    // ---- one CTA per tile: 16 batch rows per box, as many boxes in flight as the
+    // pipeline buffers hold
+    const uint32_t elt = p.out_f32 ? 4u : 2u;
+    const uint32_t grp_bytes = 16u * kTileN * elt;
+    const int G = p.m_pad / 16;
+    const int nbuf = min(G, (int)((uint32_t)p.stages * stage_bytes / grp_bytes));
+    for (int g0 = 0; g0 < G; g0 += nbuf) {
+      if (g0 > 0) {
+        if (tid == 0) tma_store_wait_read();
+        __syncthreads();
+      }
+      const int g1 = min(G, g0 + nbuf);
+      for (int g = g0; g < g1; ++g) {
+        float v[16];
+        tmem_ld16(t_lane + g * 16, v);
+        if (swiglu) {
+          float u[16];
+          tmem_ld16(t_lane + p.m_pad + g * 16, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = silu_f(v[j]) * u[j];
+        }
+        uint8_t* dst = smem_gen + (uint32_t)(g - g0) * grp_bytes;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (p.out_f32) reinterpret_cast<float*>(dst)[j * kTileN + row] = v[j];
+          else reinterpret_cast<__nv_bfloat16*>(dst)[j * kTileN + row] = __float2bfloat16_rn(v[j]);
+        }
+      }
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        for (int g = g0; g < g1; ++g)
+          if (m_base + g * 16 < p.M)
+            tma_store_2d(&tm_y, smem_base + (uint32_t)(g - g0) * grp_bytes, tile * kTileN, m_base + g * 16);
+        tma_store_commit();
+      }
+    }
+    if (tid == 0) tma_store_wait_read();
   } else if (ok_all) {
     if (p.splits == 1) {
       for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
@@ -318,6 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
+  TC_TRACE(tid == 0, 7);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)p.tmem_cols)
@@ -357,6 +490,24 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t co
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(HB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return HB_OK;
+}
+
+// Output map: [rows, cols] elements of elt bytes, row stride ld elements, box
+// [box_rows, 128 cols], no swizzle (the kernel stages rows of 128 features densely).
+static int encode_out_map(CUtensorMap* tm, void* ptr, int64_t rows, int64_t cols, int64_t ld, bool f32,
+                          int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(HB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const cuuint64_t elt = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elt};
+  cuuint32_t box[2] = {(cuuint32_t)kTileN, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(HB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
   return HB_OK;
 }
 
@@ -433,13 +584,21 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   // cluster form: power-of-two size <= 8 whose receive buffers fit the pipeline's
   // shared memory; anything else reduces through global scratch
   pl.cluster = false;
+  // the output leaves through bulk tensor stores when its rows are 16-byte multiples
+  const size_t out_elt = out_f32 ? 4 : 2;
+  pl.tma_store = ((size_t)n_rows * out_elt) % 16 == 0;
   auto recv_fits = [&](int sp) {
-    return (size_t)(sp - 1) * n_acc * pl.m_pad * (kTileN / sp) * sizeof(float) <= (size_t)pl.stages * stage;
+    // received partials [sp-1][n_acc][m_pad/sp][128] fp32 + the staged output [m_pad/sp][128]
+    const size_t cw = (size_t)pl.m_pad / sp;
+    return (size_t)(sp - 1) * n_acc * cw * kTileN * sizeof(float) + cw * kTileN * out_elt <=
+           (size_t)pl.stages * stage;
   };
-  if (want_cluster && pl.splits > 1) {
+  if (want_cluster && pl.splits > 1 && pl.tma_store) {
     if (force_splits <= 0)
-      while (pl.splits > 1 && !recv_fits(pl.splits)) pl.splits /= 2;
-    pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 && recv_fits(pl.splits);
+      while (pl.splits > 1 && (!recv_fits(pl.splits) || pl.m_pad / pl.splits < 4)) pl.splits /= 2;
+    // every partner owns m_pad / splits batch rows, exchanged four at a time
+    pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
+                 pl.m_pad / pl.splits >= 4 && recv_fits(pl.splits);
   }
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
@@ -490,28 +649,52 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
   p.cluster = pl.cluster ? 1 : 0;
+  CUtensorMap tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
+  const size_t y_elt = pl.out_f32 ? 4 : 2;
+  const bool y_ok = (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && ((size_t)ldy * y_elt) % 16 == 0;
+  if (pl.cluster && !y_ok)
+    return fail(HB_ERR_INVALID_ARG, "gemm_tc: output must be 16-byte aligned with rows of a multiple of 16 bytes");
+  p.tma_store = (pl.tma_store && y_ok && (pl.cluster || pl.splits == 1)) ? 1 : 0;
+  if (p.tma_store) {
+    const int box_rows = pl.cluster ? pl.m_pad / pl.splits : 16;
+    int rc = encode_out_map(&tm_y, Y, pl.M, pl.N, ldy, pl.out_f32, box_rows);
+    if (rc) return rc;
+  }
   { const char* sg = getenv("HB_TC_STAGGER"); p.stagger = (sg && sg[0] == '1') ? 1 : 0; }  // measured: no gain, off
   dim3 grid((unsigned)(pl.n_tiles * pl.splits), (unsigned)pl.m_tiles);
-  if (pl.cluster) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kTcThreads);
-    cfg.dynamicSmemBytes = pl.smem_bytes;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)pl.splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, pl.tm_w, pl.tm_x, p));
-  } else {
-    gemm_tc_kernel<<<grid, kTcThreads, pl.smem_bytes, st>>>(pl.tm_w, pl.tm_x, p);
-    HB_LAUNCH_CHECK();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  static const bool use_pdl = [] { const char* e = getenv("HB_PDL"); return !(e && e[0] == '0'); }();
+  if (use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
   }
+  if (pl.cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)pl.splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, pl.tm_w, pl.tm_x, tm_y, p));
   return HB_OK;
 }
 
 }  // namespace hb
+
+#ifdef HB_TC_TRACE
+extern "C" int hb_debug_tc_trace(unsigned long long* host_out, int n_ctas) {
+  if (n_ctas > hb::kTraceCtas) n_ctas = hb::kTraceCtas;
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host_out, hb::g_tc_trace, sizeof(unsigned long long) * n_ctas * hb::kTraceSlots);
+}
+#endif

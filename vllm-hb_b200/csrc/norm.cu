@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(kNormThreads)
 rms_norm_vec_kernel(T* __restrict__ out, T* __restrict__ resid_out, const T* __restrict__ x,
                     const T* __restrict__ resid_in, const T* __restrict__ w, int64_t hidden,
                     float eps) {
+  pdl_trigger();
   __shared__ float red[33];
   constexpr int N = Vec16<T>::N;
   const int64_t row = blockIdx.x;

@@ -136,15 +136,29 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
+  pdl_launch_dependents();
+  if (!(warp == 0 && lane == 0)) pdl_wait();
 
   // ------------------------------------------------------------ 1. mainloop
   if (warp == 0) {
     if (lane == 0) {
       int armed = 0;
-      for (int i = 0; i < n_kc; ++i) {
+      // weight slabs of the first stages are requested before the previous kernel is
+      // known to be finished; activations only after pdl_wait()
+      const int pre = min(p.stages, n_kc);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t full = smem_u32(&s_full[i]);
+        mbar_expect_tx(full, stage_bytes);
+        tma_load_2d(smem_base + i * stage_bytes, &tm_w, (kc0 + i) * kTileK, tile * kTileN, full);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem_base + i * stage_bytes + a_bytes, &tm_x, (kc0 + i) * kTileK, 0, smem_u32(&s_full[i]));
+      armed = pre;
+      for (int i = pre; i < n_kc; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-        if (i >= p.stages && !mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, &s_abort)) break;
+        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, &s_abort)) break;
         const uint32_t full = smem_u32(&s_full[s]);
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
@@ -182,16 +196,23 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     (i > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&s_empty[s]));
       }
-      if (ok) tc_commit(smem_u32(&s_done));
+      // only this thread polls for the accumulator; the other 127 sleep at the CTA
+      // barrier below (a polling warp occupies the SM's memory pipe, which slows the
+      // epilogue of a co-resident CTA several-fold)
+      if (ok) {
+        tc_commit(smem_u32(&s_done));
+        ok = mbar_wait(smem_u32(&s_done), 0, &s_abort);
+      }
+      if (!ok) s_abort = 1;
     }
     __syncwarp();
   }
 
-  const bool have_acc = mbar_wait(smem_u32(&s_done), 0, &s_abort);
-  tc_fence_after();
   const int row = warp * 32 + lane;  // accumulator row = feature inside the 128-wide tile
   const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const bool ok_all = __syncthreads_and(have_acc ? 1 : 0) != 0;
+  __syncthreads();
+  tc_fence_after();
+  const bool ok_all = s_abort == 0;
 
   // ------------------------------------------------------------ 2. split-K in the cluster
   // CTA r of the cluster owns features [r*FW, (r+1)*FW) of the tile = "unit" tile*S + r.
@@ -281,7 +302,8 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         uint4* dst = part_slot(q, me, u_slot);
         for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
       }
-      __threadfence_system();
+      // bar.sync orders every thread's stores before the flag threads; their system-scope
+      // release store is cumulative over them (no fence per thread needed)
       __syncthreads();
       if (tid < R && tid != me && (!p.two_shot || tid == owner_rank))
         f_st_release(&flags_of(tid)->pflag[unit * HB_MAX_RANKS + me], target);
@@ -335,7 +357,6 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int m = tid; m < p.M; m += kTcThreads) rq[(int64_t)m * u_stride] = s_rowsq[m];
         }
       }
-      __threadfence_system();
       __syncthreads();
       if (tid == 0) f_st_release(&fl->gflag[unit], target);
       if (R > 1 && p.two_shot && tid < R && tid != me) f_st_release(&flags_of(tid)->gflag[unit], target);
@@ -559,18 +580,27 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = fp.g.smem_bytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if (S > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)S;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-  } else {
-    attr[0].id = cudaLaunchAttributeCooperative;  // co-residency checked by the driver
-    attr[0].val.cooperative = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)S;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  static const bool use_pdl = [] { const char* e = getenv("HB_PDL"); return !(e && e[0] == '0'); }();
+  if (use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  } else if (S == 1) {
+    attr[na].id = cudaLaunchAttributeCooperative;  // co-residency checked by the driver
+    attr[na].val.cooperative = 1;
+    ++na;
   }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = na;
   if (S > 1) {
     // CTAs of this grid wait for one another: every cluster must be resident at once
     int max_clusters = 0;

@@ -55,6 +55,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Bulk tensor store shared -> global (box of the tensor map at element coordinates
+// x, y); rows and columns outside the tensor are clipped.  x * element size must be a
+// multiple of 16 bytes and the coordinates non-negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(tm), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once every committed store has finished READING shared memory (the buffer
+// may be reused or the CTA may exit); the global writes complete with the grid.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Orders this thread's shared-memory writes before later async-proxy (TMA) reads.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -107,6 +121,15 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
          ((uint32_t)(kTileN >> 4) << 24);
 }
 
+// ---- programmatic dependent launch: a kernel launched with the attribute may start
+// while its predecessor in the stream is still running; it must not touch memory the
+// predecessor produces (or still reads) before pdl_wait() returns.  Both are no-ops for
+// a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- thread-block cluster helpers (split-K partners exchange accumulators on chip)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -122,12 +145,19 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void st_cluster_f32(uint32_t caddr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(caddr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void st_cluster_v4(uint32_t caddr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
 // Every thread of every CTA of the cluster arrives; hardware barrier, always reached.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
+// silu(z) = z / (1 + e^-z) with the fast divide: the 16 activations of an accumulator
+// group must not cost more than the group's loads (the IEEE divide is ~20 dependent
+// instructions); the quotient is rounded to bf16 afterwards.
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.f + __expf(-z)); }
 
 }  // namespace hb
