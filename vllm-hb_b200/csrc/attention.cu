@@ -305,16 +305,38 @@ static int dispatch_nrep(int nrep, cudaStream_t st, T* out, float* po, float* pm
   }
 }
 
-// Internal entry: q rows may sit inside a wider [q|k|v] projection buffer.
+// Tensor-core kernel (attention_mma.cu): bf16, head_dim 128, up to 16 query heads per kv head.
+bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                   int nrep, int head_dim, int64_t num_blocks, int hkv, hb_dtype dtype);
+int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
+                        int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
+                        const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
+                        int64_t num_blocks, int n_splits, int* err_flag);
+
+// Internal entry: q rows may sit inside a wider [q|k|v] projection buffer.  err_flag
+// (device int, may be null) is raised when a bounded wait of the tensor-core kernel ran out.
 int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride, const void* k_cache,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype) {
+                    hb_dtype dtype, int* err_flag) {
   if (n_seqs == 0) return HB_OK;
   const int nrep = n_q_heads / n_kv_heads;
   float* po = (float*)workspace;
   float* pml = po ? po + (size_t)n_seqs * n_q_heads * n_splits * head_dim : nullptr;
+  static const bool force_simt = [] { const char* e = getenv("HB_ATTN"); return e && e[0] == 's'; }();
+  if (!force_simt && paged_attention_mma_supported(q, q_stride, k_cache, v_cache, nrep, head_dim, num_blocks,
+                                                   n_kv_heads, dtype)) {
+    int rc = paged_attention_mma(st, out, po, pml, q, q_stride, k_cache, v_cache, block_tables, ctx_lens, n_seqs,
+                                 n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, err_flag);
+    if (rc) return rc;
+    if (n_splits > 1) {
+      attn_merge_kernel<__nv_bfloat16><<<(unsigned)(n_seqs * n_q_heads), 128, 0, st>>>(
+          (__nv_bfloat16*)out, po, pml, n_splits, head_dim);
+      HB_LAUNCH_CHECK();
+    }
+    return HB_OK;
+  }
   HB_DISPATCH_DTYPE(dtype, T, {
     if (head_dim == 128)
       return (dispatch_nrep<T, 128>(nrep, st, (T*)out, po, pml, (const T*)q, (const T*)k_cache,
@@ -354,7 +376,7 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
   HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention: bad block counts");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads,
-                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype);
+                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr);
 }
 
 }  // extern "C"
@@ -419,7 +441,7 @@ int hb_paged_decode_attention_static(void* stream, void* out, const void* q, con
   if (rc) return rc;
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache, v_cache,
                              block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype);
+                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr);
 }
 
 }  // extern "C"

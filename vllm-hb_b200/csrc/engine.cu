@@ -300,6 +300,7 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = hb_rope_inv_freq((float)e->theta, (int)e->hd, inv.data()))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_inv_freq, inv.size() * 4))) return rc;
   HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
+  if ((rc = paged_attention_mma_prepare())) return rc;
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
   // A single rank has nothing to reduce: GEMM followed by add+norm is the faster
@@ -324,8 +325,11 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
 static int pick_attn_splits(const hb_engine* e, int B) {
   DeviceInfo di;
   if (device_info(e->device, &di)) return 1;
+  // A split costs a partial write and the merge kernel: only worth it when the
+  // (sequence, kv head) units alone leave most SMs idle (measured).
   const int64_t units = (int64_t)B * e->hkv_l;
-  int s = (int)((2 * (int64_t)di.sm_count + units - 1) / units);
+  if (units * 3 >= 2 * (int64_t)di.sm_count) return 1;
+  int s = (int)(((int64_t)di.sm_count + units - 1) / units);
   return std::max(1, std::min(s, 16));
 }
 
@@ -428,7 +432,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype))) return rc;
+                              e->dtype, e->d_err))) return rc;
     e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);

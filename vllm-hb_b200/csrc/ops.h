@@ -9,7 +9,10 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype);
+                    hb_dtype dtype, int* err_flag = nullptr);
+// Opts the tensor-core attention kernel in to its shared memory (once per device,
+// outside any stream capture).
+int paged_attention_mma_prepare();
 
 // RoPE on the q and k parts of a fused [q | k | v] projection row and the paged KV
 // write in one pass: q is rotated in place, rotated k and v go straight to their slot.
