@@ -74,7 +74,12 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu_index, self.rows, self.proc = gpu_index, [], None
+        self.gpu_index, self.rows, self.proc, self.t_begin = gpu_index, [], None, 0.0
+
+    def begin_region(self):
+        """Samples that arrive from now on count (nvidia-smi is started earlier: its own
+        start-up takes longer than a short timed region)."""
+        self.t_begin = time.time()
 
     def start(self):
         try:
@@ -87,7 +92,7 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -99,8 +104,8 @@ class ClockSampler:
             pass
         sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            if len(r) < 9:
+        for t_arrival, r in self.rows:
+            if len(r) < 9 or t_arrival < self.t_begin:
                 continue
             try:
                 sm.append(float(r[1])); smax.append(float(r[2])); power.append(float(r[3]))
@@ -235,6 +240,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     # prefill: the prompts go through the same decode step in lock-step (untimed)
     nxt = np.empty(B, dtype=np.uint32)
     for t in range(P):
@@ -242,10 +250,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     for _ in range(W):
         eng.decode_batch(seqs, nxt.copy(), next_tokens=nxt)
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     barrier()
+    sampler.begin_region()
     dev_ms = 0.0
     ctx_sum = 0
     t0 = time.perf_counter()
@@ -283,6 +289,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         e2e = tokens / (wall_ms / 1e3)
         gemm_ms = prof.get("gemm", 0.0)
         achieved = gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else None
+        # DRAM bytes (read + write) of the GEMM launches of one step, from the ncu captures
+        # summarised in profiles/gemm_tc_kernel_decode_shapes.md: per layer qkv 50.96 MB,
+        # o_proj 34.15, gate|up 239.4, down_proj 123.1, plus lm_head 1085.8.  Only the
+        # full-size single-GPU workload was captured.
+        traffic = None
+        if world == 1 and B == 64 and shape["num_hidden_layers"] == 32 and shape["hidden_size"] == 4096 \
+                and shape["intermediate_size"] == 14336 and shape["vocab_size"] == 128256:
+            traffic = (32 * (50.96 + 34.15 + 239.4 + 123.1) + 1085.8) * 1e6
         h2d = 4 * B * 3 + 8 * B + 4 * B * ((max_seq + 15) // 16)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -297,8 +311,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (all GEMM launches of a step)",
                          "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
-                         "algorithmic_bytes_per_step": gemm_bytes, "ms_per_step": gemm_ms},
+                         "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                         "algorithmic_bytes_per_step": gemm_bytes, "ms_per_step": gemm_ms,
+                         "timing": "CUDA events between the kernels of eager (ungraphed) steps on the engine stream"},
             "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1e3) / 1e9,
                               "frac": step_bytes / (dev_ms / K / 1e3) / 1e9 / peak},
             "kernel_ms_per_step": prof,

@@ -125,9 +125,12 @@ def test_fused_rowparallel(hb, worlds, M, N, K_, algo):
             assert np.array_equal(host(res), host(outs[0][1])) and np.array_equal(host(normed), host(outs[0][0]))
 
 
-def test_tp_engine_matches_oracle(hb, worlds):
+@pytest.mark.parametrize("fused", ["0", "1"])
+def test_tp_engine_matches_oracle(hb, worlds, fused, monkeypatch):
     """A small bf16 model sharded over the ranks: logits of every rank against the
-    oracle with the same world size."""
+    oracle with the same world size, with the row-parallel projections as separate
+    kernels (fused=0) and as the one-kernel fused form (fused=1)."""
+    monkeypatch.setenv("HB_FUSED", fused)
     from oracle import llama_ref as R_
 
     R = len(worlds)

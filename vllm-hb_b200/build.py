@@ -45,12 +45,12 @@ def _headers_mtime() -> float:
     return max(h.stat().st_mtime for h in hs)
 
 
-def _compile(src: Path, force: bool, verbose: bool) -> Path:
-    obj = OBJ_DIR / (src.name + ".o")
+def _compile(src: Path, force: bool, verbose: bool, obj_dir: Path = OBJ_DIR, defines: tuple = ()) -> Path:
+    obj = obj_dir / (src.name + ".o")
     newest_dep = max(src.stat().st_mtime, _headers_mtime())
     if not force and obj.exists() and obj.stat().st_mtime >= newest_dep:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", str(src), "-o", str(obj)]
     if src.suffix == ".cc":
         cmd.insert(1, "-x")
         cmd.insert(2, "cu")
@@ -66,22 +66,28 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    OBJ_DIR.mkdir(exist_ok=True)
+def build(force: bool = False, verbose: bool = False, variant: str = "") -> Path:
+    """variant "trace": the library with -DHB_TC_TRACE (phase timestamps inside the GEMM
+    kernel, read by trace_gemm.py), built beside the product as libhb_trace.so."""
+    obj_dir = OBJ_DIR if not variant else HERE / f"build_{variant}"
+    lib = LIB if not variant else HERE / f"libhb_{variant}.so"
+    defines = {"": (), "trace": ("HB_TC_TRACE",)}[variant]
+    obj_dir.mkdir(exist_ok=True)
     srcs = _sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, force, verbose), srcs))
-    if force or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-ldl", "-lpthread"]
+        objs = list(ex.map(lambda s: _compile(s, force, verbose, obj_dir, defines), srcs))
+    if force or not lib.exists() or any(o.stat().st_mtime > lib.stat().st_mtime for o in objs):
+        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs), "-ldl", "-lpthread"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--variant", default="", choices=["", "trace"])
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.variant))

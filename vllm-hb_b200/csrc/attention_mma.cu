@@ -71,6 +71,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                       int64_t q_stride, int* err_flag) {
   constexpr int kMmaAttnWarps = NW, kMmaAttnThreads = NW * 32;
   pdl_trigger();
+  pdl_grid_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kMmaAttnWarps][kAttnStages];
   __shared__ int s_abort;
@@ -397,15 +398,14 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
     if (ev[0] == '4') nw = 4;
   }
   if (nw == 2) {
-    paged_attn_mma_kernel<2><<<grid, 64, mma_attn_smem(2), st>>>(
-        tm_k, tm_v, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq, hkv,
-        hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag);
+    HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
+                             (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag));
   } else {
-    paged_attn_mma_kernel<4><<<grid, 128, mma_attn_smem(4), st>>>(
-        tm_k, tm_v, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq, hkv,
-        hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag);
+    HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<4>, grid, dim3(128), mma_attn_smem(4), st, tm_k, tm_v,
+                             (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag));
   }
-  HB_LAUNCH_CHECK();
   return HB_OK;
 }
 

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "../../include/hb.h"
@@ -37,6 +38,32 @@ inline bool dtype_valid(int d) { return d == HB_F32 || d == HB_F16 || d == HB_BF
   } while (0)
 
 #define HB_LAUNCH_CHECK() HB_CUDA_CHECK(cudaGetLastError())
+
+#ifdef __CUDACC__
+// Launch with programmatic stream serialisation: the grid may become resident while the
+// preceding kernel of the stream is still draining, which hides the launch latency of
+// the small kernels of a decode step.  The kernel must call pdl_grid_wait() before it
+// touches global memory.  HB_PDL=0 launches normally.
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("HB_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 // Dispatch a generic lambda on the element type.
 #define HB_DISPATCH_DTYPE(dtype, T, ...)                                   \
@@ -80,6 +107,10 @@ template <typename T> struct Vec16 {
 // programmatic-serialisation attribute begin its prologue (it still waits for this
 // grid to finish before it reads what this grid writes).  A no-op otherwise.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Blocks until the preceding grid of the stream has completed and its writes are
+// visible; returns at once for a kernel launched without the attribute.  A kernel that
+// launch_pdl() starts must pass here before its first global read or write.
+__device__ __forceinline__ void pdl_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -19,6 +19,8 @@ rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                const float* __restrict__ inv_freq, int nq, int nkv, int hd, int64_t num_blocks) {
   __shared__ float s_cos[256];
   __shared__ float s_sin[256];
+  pdl_trigger();
+  pdl_grid_wait();
   constexpr int N = Vec16<T>::N;
   const int64_t t = blockIdx.x;
   const int half = hd >> 1;
@@ -86,11 +88,10 @@ int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
     if ((head_dim / 2) % Vec16<T>::N != 0)
       return fail(HB_ERR_INVALID_ARG, "rope_kv_write: head_dim %d too small for 128-bit vectors",
                   head_dim);
-    rope_kv_kernel<T><<<(unsigned)n_tokens, kRkThreads, 0, st>>>(
-        (T*)qkv, (T*)k_cache, (T*)v_cache, positions, slot_mapping, inv_freq, n_q_heads, n_kv_heads,
-        head_dim, num_blocks);
+    HB_CUDA_CHECK(launch_pdl(rope_kv_kernel<T>, dim3((unsigned)n_tokens), dim3(kRkThreads), 0, st, (T*)qkv,
+                             (T*)k_cache, (T*)v_cache, positions, slot_mapping, inv_freq, n_q_heads, n_kv_heads,
+                             head_dim, num_blocks));
   });
-  HB_LAUNCH_CHECK();
   return HB_OK;
 }
 

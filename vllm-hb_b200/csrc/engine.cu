@@ -303,12 +303,12 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = paged_attention_mma_prepare())) return rc;
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
-  // A single rank has nothing to reduce: GEMM followed by add+norm is the faster
-  // sequence there (measured).  HB_UNFUSED=1 / HB_FUSED=1 force either path.
-  const char* uf = getenv("HB_UNFUSED");
+  // The row-parallel projections run as GEMM -> peer-memory all-reduce -> add+norm by
+  // default: measured at 1 and 2 ranks that sequence is still ahead of the one-kernel
+  // fused form (whose grid-wide wait costs more than the two kernel boundaries it
+  // saves).  HB_FUSED=1 selects the fused kernel.
   const char* ff = getenv("HB_FUSED");
-  e->use_fused = e->use_tc && e->ws > 1 && !(uf && uf[0] == '1');
-  if (e->use_tc && ff && ff[0] == '1') e->use_fused = true;
+  e->use_fused = e->use_tc && ff && ff[0] == '1';
   if (e->use_fused) {
     const size_t fw = std::max(rowpar_fused_workspace_bytes(B, e->H, e->hq_l * e->hd),
                                rowpar_fused_workspace_bytes(B, e->H, e->I_l));

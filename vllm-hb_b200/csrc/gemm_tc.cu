@@ -208,8 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tc_commit(smem_u32(&s_empty[s]));  // frees the stage once these MMAs have read it
       }
       // only this thread polls for the accumulator; the other 127 sleep at the CTA
-      // barrier below (a polling warp occupies the SM's memory pipe, which slows the
-      // epilogue of a co-resident CTA several-fold)
+      // barrier below
       if (ok) {
         tc_commit(smem_u32(&s_done));
         ok = mbar_wait(smem_u32(&s_done), 0, &s_abort);
@@ -594,11 +593,33 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
            (size_t)pl.stages * stage;
   };
   if (want_cluster && pl.splits > 1 && pl.tma_store) {
-    if (force_splits <= 0)
-      while (pl.splits > 1 && (!recv_fits(pl.splits) || pl.m_pad / pl.splits < 4)) pl.splits /= 2;
+    // The exchange buffers of a wide batch (or of the two SwiGLU accumulators) may not
+    // fit the two-CTAs-per-SM budget.  When a split factor yields at most one CTA per SM
+    // anyway, it may take a deeper pipeline (one CTA per SM) instead of being halved: a
+    // matrix with few row slabs needs the splits to reach the SMs.
+    if (force_splits <= 0) {
+      const int small_stages = pl.stages;
+      const size_t big = 200 * 1024;
+      const int big_stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, big / stage));
+      const bool big_ok = !getenv("HB_TC_SMEM_KB") && big_stages > small_stages &&
+                          (size_t)big_stages * stage + 1024 <= di.smem_optin;
+      while (pl.splits > 1) {
+        if (pl.m_pad / pl.splits >= 4 && pl.m_pad % (4 * pl.splits) == 0) {
+          pl.stages = small_stages;
+          if (recv_fits(pl.splits)) break;
+          if (big_ok && (int64_t)pl.n_tiles * pl.m_tiles * pl.splits <= di.sm_count) {
+            pl.stages = big_stages;
+            if (recv_fits(pl.splits)) break;
+          }
+        }
+        pl.stages = small_stages;
+        pl.splits /= 2;
+      }
+      pl.smem_bytes = pl.stages * stage + 1024;
+    }
     // every partner owns m_pad / splits batch rows, exchanged four at a time
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
-                 pl.m_pad / pl.splits >= 4 && recv_fits(pl.splits);
+                 pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so

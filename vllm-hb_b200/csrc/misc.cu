@@ -59,12 +59,35 @@ argmax_kernel(uint32_t* __restrict__ out, const T* __restrict__ logits, int64_t 
   const T* row = logits + (int64_t)blockIdx.x * vocab;
   float best = -FLT_MAX;
   uint32_t bi = 0xffffffffu;
-  for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = to_f32<T>(row[i]);
-    // NaN never wins; strictly greater keeps the earliest index within a thread
+  // NaN never wins; strictly greater keeps the earliest index within a thread (a thread
+  // visits its elements in increasing index order on both paths)
+  auto take = [&](float v, int64_t i) {
     if (v > best || bi == 0xffffffffu) {
       if (v == v) { best = v; bi = (uint32_t)i; }
     }
+  };
+  constexpr int N = Vec16<T>::N;
+  if (vocab % N == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 128-bit loads, four independent ones in flight per thread
+    const int64_t nvec = vocab / N;
+    const int64_t step = blockDim.x;
+    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * step) {
+      Vec16<T> a[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * step < nvec) a[u].load(row + (v0 + u * step) * N);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * step < nvec) {
+          float f[N];
+          a[u].unpack(f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) take(f[j], (v0 + u * step) * N + j);
+        }
+      }
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) take(to_f32<T>(row[i]), i);
   }
   auto better = [](float v, uint32_t i, float bv, uint32_t bidx) {
     return (i != 0xffffffffu) && (bidx == 0xffffffffu || v > bv || (v == bv && i < bidx));

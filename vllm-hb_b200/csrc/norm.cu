@@ -21,6 +21,7 @@ rms_norm_vec_kernel(T* __restrict__ out, T* __restrict__ resid_out, const T* __r
                     const T* __restrict__ resid_in, const T* __restrict__ w, int64_t hidden,
                     float eps) {
   pdl_trigger();
+  pdl_grid_wait();
   __shared__ float red[33];
   constexpr int N = Vec16<T>::N;
   const int64_t row = blockIdx.x;
@@ -143,8 +144,8 @@ static int launch_norm(cudaStream_t st, T* out, T* resid_out, const T* x, const 
   const bool vec = hidden % N == 0 && aligned(out) && aligned(x) && aligned(w) &&
                    (!ADD || (aligned(resid_out) && aligned(resid_in)));
   if (vec)
-    rms_norm_vec_kernel<T, ADD><<<(unsigned)rows, kNormThreads, 0, st>>>(out, resid_out, x, resid_in,
-                                                                        w, hidden, eps);
+    HB_CUDA_CHECK(launch_pdl(rms_norm_vec_kernel<T, ADD>, dim3((unsigned)rows), dim3(kNormThreads), 0, st, out,
+                             resid_out, x, resid_in, w, hidden, eps));
   else
     rms_norm_scalar_kernel<T, ADD><<<(unsigned)rows, kNormThreads, 0, st>>>(out, resid_out, x,
                                                                            resid_in, w, hidden, eps);

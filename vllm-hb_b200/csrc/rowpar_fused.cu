@@ -11,9 +11,10 @@
 // thread-block cluster:
 //   1. tcgen05 mainloop (TMA -> shared memory -> UMMA, fp32 accumulator in tensor
 //      memory), exactly the decode GEMM: the weight slab is the UMMA A operand.
-//   2. split-K on chip: CTA s owns the 128/S features [s*FW, (s+1)*FW) of the tile — the
-//      "unit" t*S+s; partners send it their accumulator rows through distributed shared
-//      memory and it adds the S partials in split order.
+//   2. split-K on chip: CTA s owns the batch rows [s*CW, (s+1)*CW), CW = m_pad/S, of the
+//      tile for all 128 features — the "unit" t*S+s; partners send it their accumulator
+//      columns through distributed shared memory (16-byte stores) and it adds the S
+//      partials in split order.
 //   3. every CTA rounds its unit of the rank's partial to bf16 (the reference's partials
 //      are bf16 tensors), keeps it in shared memory and PUSHES it with coalesced 128-bit
 //      stores into the staging buffer of the unit's reducer rank(s) over NVLink, then
@@ -21,11 +22,11 @@
 //      one-shot: every rank reduces every unit (one NVLink hop, R-1 times the bytes).
 //   4. a reducer waits for the R-1 remote partials of its unit, sums all R in rank
 //      order in fp32 on top of the residual, rounds, writes resid_out, accumulates the
-//      per-row sum of squares of the rounded unit, and (two-shot) pushes the reduced
-//      unit and the row sums to every peer, then raises gflag[u] everywhere.
-//   5. every CTA waits until all U units (hence all row sums) are present locally,
-//      computes the row scales and writes its unit of normed_out (non-reducers also copy
-//      the gathered unit into resid_out).
+//      sum of squares of the unit's rows over its 128 features, and (two-shot) pushes the
+//      reduced unit and the row sums to every peer, then raises gflag[u] everywhere.
+//   5. every CTA waits until the units of ITS batch rows are present locally for every
+//      tile (N/128 flags), sums their row sums into the row scales and writes its unit
+//      of normed_out (non-reducers also copy the gathered unit into resid_out).
 // Flags carry the device-resident call sequence number, so a captured CUDA graph can
 // replay the kernel; staging reuse is guarded by the per-rank "done" flags shared with
 // the all-reduce kernel.  CTAs wait for other CTAs of the same grid, so the grid never
@@ -53,7 +54,7 @@ struct FusedParams {
   float* partials;                     // split-K scratch [tile][split][m_pad][128] fp32
   int* counters;                       // [n_tiles], zero between launches
   void* peer[HB_MAX_RANKS];            // staging base of every rank (flags + data)
-  int64_t tile_bytes;                  // M * 128 * 2
+  int64_t tile_bytes;                  // one unit: (m_pad / splits) * 128 * 2
   int64_t gather_off, rowsq_off;       // byte offsets inside the data area
 };
 
@@ -197,8 +198,7 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tc_commit(smem_u32(&s_empty[s]));
       }
       // only this thread polls for the accumulator; the other 127 sleep at the CTA
-      // barrier below (a polling warp occupies the SM's memory pipe, which slows the
-      // epilogue of a co-resident CTA several-fold)
+      // barrier below
       if (ok) {
         tc_commit(smem_u32(&s_done));
         ok = mbar_wait(smem_u32(&s_done), 0, &s_abort);
@@ -215,37 +215,42 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const bool ok_all = s_abort == 0;
 
   // ------------------------------------------------------------ 2. split-K in the cluster
-  // CTA r of the cluster owns features [r*FW, (r+1)*FW) of the tile = "unit" tile*S + r.
-  // Partners send the accumulator rows they do not own to the owner through distributed
-  // shared memory; the owner adds the S partials in split order, rounds to bf16 (the
-  // reference's partials are bf16 tensors) and leaves its unit [M][FW] in shared memory.
-  const int S = p.splits, FW = kTileN / S;
-  const int owner = row / FW, f_loc = row % FW;
-  float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][m_pad][FW] fp32
-  const int slot_floats = p.m_pad * FW;
+  // CTA r of the cluster owns the batch rows [r*CW, (r+1)*CW) of the tile for all 128
+  // features = "unit" tile*S + r.  Partners send the accumulator columns they do not
+  // own to the owner through distributed shared memory (16-byte stores, four columns at
+  // a time); the owner adds the S partials in split order, rounds to bf16 (the
+  // reference's partials are bf16 tensors) and leaves its unit [CW][128] in shared memory.
+  const int S = p.splits, CW = p.m_pad / S;
+  float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][CW/4][128 features][4 columns] fp32
+  const int slot_floats = CW * kTileN;
   const uint32_t recv_bytes = (uint32_t)((S - 1) * slot_floats * 4);
-  __nv_bfloat16* tile_s = reinterpret_cast<__nv_bfloat16*>(smem_gen + recv_bytes);  // [M][FW] bf16
-  uint4* tile_u4 = reinterpret_cast<uint4*>(smem_gen + recv_bytes);
-  const int own_lo = (warp * 32) / FW, own_hi = (warp * 32 + 31) / FW;
-  const bool warp_sends = !(own_lo == split && own_hi == split);
-  const bool warp_owns = own_lo <= split && split <= own_hi;
+  __nv_bfloat16* unit_s = reinterpret_cast<__nv_bfloat16*>(smem_gen + recv_bytes);  // [CW][128] bf16
+  uint4* unit_u4 = reinterpret_cast<uint4*>(smem_gen + recv_bytes);
+  const int r0 = split * CW;                          // first batch row of the unit
+  const int rows_valid = max(0, min(CW, p.M - r0));   // rows of the unit inside the batch
   if (S > 1) {
     cluster_sync_all();  // every partner's pipeline buffers are idle from here on
-    if (ok_all && warp_sends) {
-      const int slot = split < owner ? split : split - 1;
-      const uint32_t dst0 = cluster_map(smem_base + (uint32_t)(slot * slot_floats + f_loc) * 4u, (uint32_t)owner);
+    if (ok_all) {
       for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+        if (c0 / CW == split && (c0 + 15) / CW == split) continue;  // uniform over the CTA
         float v[16];
-        tmem_ld16(t_lane + c0, v);  // warp-collective: lanes are masked at the store only
+        tmem_ld16(t_lane + c0, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (owner != split) st_cluster_f32(dst0 + (uint32_t)((c0 + j) * FW) * 4u, v[j]);
+        for (int q = 0; q < 4; ++q) {
+          const int c = c0 + 4 * q, owner = c / CW;
+          if (owner != split) {
+            const int slot = split < owner ? split : split - 1;
+            const uint32_t local =
+                smem_base + (uint32_t)(slot * slot_floats + (((c % CW) >> 2) * kTileN + row) * 4) * 4u;
+            st_cluster_v4(cluster_map(local, (uint32_t)owner), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+        }
       }
     }
-    cluster_sync_all();  // release/acquire: rows sent above are visible to their owner
+    cluster_sync_all();  // release/acquire: columns sent above are visible to their owner
   }
-  if (ok_all && warp_owns) {
-    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+  if (ok_all) {
+    for (int c0 = r0 & ~15; c0 < r0 + CW; c0 += 16) {
       float own[16], g[16];
       tmem_ld16(t_lane + c0, own);
 #pragma unroll
@@ -255,15 +260,21 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
           for (int j = 0; j < 16; ++j) g[j] += own[j];
         } else {
-          const float* rs = recv + (src < split ? src : src - 1) * slot_floats + f_loc;
+          const float* rs = recv + (src < split ? src : src - 1) * slot_floats;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) g[j] += rs[(c0 + j) * FW];
+          for (int q = 0; q < 4; ++q) {
+            const int cl = c0 + 4 * q - r0;
+            if (cl >= 0 && cl < CW) {
+              const float4 t = *reinterpret_cast<const float4*>(rs + ((cl >> 2) * kTileN + row) * 4);
+              g[4 * q] += t.x; g[4 * q + 1] += t.y; g[4 * q + 2] += t.z; g[4 * q + 3] += t.w;
+            }
+          }
         }
       }
-      if (owner == split) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < p.M) tile_s[(c0 + j) * FW + f_loc] = __float2bfloat16_rn(g[j]);
+      for (int j = 0; j < 16; ++j) {
+        const int cl = c0 + j - r0;
+        if (cl >= 0 && cl < CW) unit_s[cl * kTileN + row] = __float2bfloat16_rn(g[j]);
       }
     }
   }
@@ -274,10 +285,10 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   bool proto_ok = ok_all;
   const int R = p.ws, me = p.rank;
   const int unit = tile * S + split, U = p.n_tiles * S;
-  const int u_stride = (U + 3) & ~3;  // row stride of the [m][unit] row-sum table
-  const int lpr = FW / 8;            // 16-byte vectors (lanes) per batch row of the unit
-  const int n_u4 = p.M * lpr;
-  const int n0 = tile * kTileN + split * FW;  // first feature of the unit
+  const int t_stride = (p.n_tiles + 3) & ~3;  // row stride of the [batch row][tile] row-sum table
+  constexpr int lpr = kTileN / 8;            // 16-byte vectors (lanes) per batch row of the unit
+  const int n_u4 = rows_valid * lpr;
+  const int n0 = tile * kTileN;              // first feature of the unit
   if (tid == 0) s_seq = *reinterpret_cast<volatile uint32_t*>(&fl->seq);
   __syncthreads();
   const uint32_t seq = s_seq, target = seq + 1;
@@ -300,7 +311,7 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int q = 0; q < R; ++q) {
         if (q == me || (p.two_shot && q != owner_rank)) continue;
         uint4* dst = part_slot(q, me, u_slot);
-        for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
+        for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = unit_u4[i];
       }
       // bar.sync orders every thread's stores before the flag threads; their system-scope
       // release store is cumulative over them (no fence per thread needed)
@@ -318,16 +329,17 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
     if (proto_ok) {
+      // 16 consecutive lanes hold one batch row of the unit (256 bytes)
       for (int i0 = 0; i0 < n_u4; i0 += kTcThreads) {
         const int i = i0 + tid;
         float ss = 0.f;
         if (i < n_u4) {
-          const int m = i / lpr, c = i % lpr;
+          const int m = r0 + i / lpr, c = i % lpr;
           const int64_t g_off = (int64_t)m * p.N + n0 + c * 8;
           float acc[8], t8[8];
           bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.resid_in + g_off), acc);
           for (int src = 0; src < R; ++src) {
-            const uint4 raw = (src == me) ? tile_u4[i] : __ldcg(part_slot(me, src, u_slot) + i);
+            const uint4 raw = (src == me) ? unit_u4[i] : __ldcg(part_slot(me, src, u_slot) + i);
             bf16x8_to_f32(raw, t8);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] += t8[j];
@@ -336,25 +348,24 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           bf16x8_to_f32(out, t8);  // the norm sees the rounded residual
 #pragma unroll
           for (int j = 0; j < 8; ++j) ss += t8[j] * t8[j];
-          tile_u4[i] = out;
+          unit_u4[i] = out;
           *reinterpret_cast<uint4*>(p.resid_out + g_off) = out;
         }
-        // lpr consecutive lanes hold one batch row of the unit (lpr is 2, 4, 8 or 16)
         for (int o = lpr >> 1; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (i < n_u4 && (i % lpr) == 0) s_rowsq[i / lpr] = ss;
       }
       __syncthreads();
-      // row sums are kept [m][unit] (unit fastest) so that a reader sums a batch row with
-      // 128-bit loads
-      float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + unit;
-      for (int m = tid; m < p.M; m += kTcThreads) my_rowsq[(int64_t)m * u_stride] = s_rowsq[m];
+      // row sums are kept [batch row][tile] (tile fastest) so that a reader sums a row
+      // with 128-bit loads
+      float* my_rowsq = reinterpret_cast<float*>(data_of(me) + p.rowsq_off) + tile;
+      for (int m = tid; m < rows_valid; m += kTcThreads) my_rowsq[(int64_t)(r0 + m) * t_stride] = s_rowsq[m];
       if (R > 1 && p.two_shot) {
         for (int q = 0; q < R; ++q) {
           if (q == me) continue;
           uint4* dst = reinterpret_cast<uint4*>(data_of(q) + p.gather_off + (int64_t)unit * p.tile_bytes);
-          for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = tile_u4[i];
-          float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + unit;
-          for (int m = tid; m < p.M; m += kTcThreads) rq[(int64_t)m * u_stride] = s_rowsq[m];
+          for (int i = tid; i < n_u4; i += kTcThreads) dst[i] = unit_u4[i];
+          float* rq = reinterpret_cast<float*>(data_of(q) + p.rowsq_off) + tile;
+          for (int m = tid; m < rows_valid; m += kTcThreads) rq[(int64_t)(r0 + m) * t_stride] = s_rowsq[m];
         }
       }
       __syncthreads();
@@ -363,62 +374,55 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
   }
 
-  // ---- 5. all units present -> row scales -> normalise this unit
+  // ---- 5. the units of this row group are present for every tile -> row scales ->
+  //         normalise this unit
   if (proto_ok) {
     bool ok = true;
-    for (int u2 = tid; u2 < U; u2 += kTcThreads) ok = ok && f_wait_ge(&fl->gflag[u2], target);
+    for (int t2 = tid; t2 < p.n_tiles; t2 += kTcThreads) ok = ok && f_wait_ge(&fl->gflag[t2 * S + split], target);
     proto_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
   if (proto_ok) {
-    // sum of squares of every batch row over all units: tpr threads per row, each with
-    // eight independent 128-bit loads in flight, partials combined in a fixed order
+    // sum of squares of the unit's batch rows over all tiles: tpr threads per row, 128-bit
+    // loads, partials combined in a fixed order
     const float* rowsq = reinterpret_cast<const float*>(data_of(me) + p.rowsq_off);
-    const int tpr = p.M >= kTcThreads ? 1 : (kTcThreads / p.M >= 4 ? 4 : (kTcThreads / p.M >= 2 ? 2 : 1));
-    const int u4_total = U >> 2;
-    for (int m0 = 0; m0 < p.M; m0 += kTcThreads / tpr) {
+    int tpr = 1;  // power of two, tpr * CW <= 128
+    while (tpr < 32 && tpr * 2 * CW <= kTcThreads) tpr *= 2;
+    const int t4_total = t_stride >> 2;
+    for (int m0 = 0; m0 < CW; m0 += kTcThreads / tpr) {
       const int m = m0 + tid / tpr, part = tid % tpr;
-      float a[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) a[j] = 0.f;
-      if (m < p.M) {
-        const float4* r4 = reinterpret_cast<const float4*>(rowsq + (int64_t)m * u_stride);
-        for (int i = part * 8; i < u4_total; i += tpr * 8) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (i + j < u4_total) {
-              const float4 v = __ldcg(r4 + i + j);
-              a[j] += (v.x + v.y) + (v.z + v.w);
-            }
-          }
+      float a = 0.f;
+      if (m < rows_valid) {
+        const float4* r4 = reinterpret_cast<const float4*>(rowsq + (int64_t)(r0 + m) * t_stride);
+        for (int i = part; i < t4_total; i += tpr) {
+          const float4 v = __ldcg(r4 + i);
+          const int t2 = i << 2;  // entries past the last tile are never written: mask them
+          a += ((t2 < p.n_tiles ? v.x : 0.f) + (t2 + 1 < p.n_tiles ? v.y : 0.f)) +
+               ((t2 + 2 < p.n_tiles ? v.z : 0.f) + (t2 + 3 < p.n_tiles ? v.w : 0.f));
         }
-        if (part == 0)
-          for (int u2 = u4_total << 2; u2 < U; ++u2) a[0] += __ldcg(rowsq + (int64_t)m * u_stride + u2);
       }
-      float s = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-      // tpr is 1, 2 or 4 and divides the warp: combine the partials of a row
-      for (int o = tpr >> 1; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (m < p.M && part == 0) s_rs[m] = rsqrtf(s / (float)p.N + p.eps);
+      for (int o = tpr >> 1; o >= 1; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (m < rows_valid && part == 0) s_rs[m] = rsqrtf(a / (float)p.N + p.eps);
     }
     if (!reducer) {
       const uint4* src = reinterpret_cast<const uint4*>(data_of(me) + p.gather_off + (int64_t)unit * p.tile_bytes);
       for (int i = tid; i < n_u4; i += kTcThreads) {
         const uint4 v = __ldcg(src + i);
-        tile_u4[i] = v;
-        const int m = i / lpr, c = i % lpr;
+        unit_u4[i] = v;
+        const int m = r0 + i / lpr, c = i % lpr;
         *reinterpret_cast<uint4*>(p.resid_out + (int64_t)m * p.N + n0 + c * 8) = v;
       }
     }
     __syncthreads();
     if (p.normed_out) {
       for (int i = tid; i < n_u4; i += kTcThreads) {
-        const int m = i / lpr, c = i % lpr;
+        const int ml = i / lpr, c = i % lpr;
         float h[8], w8[8];
-        bf16x8_to_f32(tile_u4[i], h);
+        bf16x8_to_f32(unit_u4[i], h);
         bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.norm_w + n0 + c * 8), w8);
-        const float r = s_rs[m];
+        const float r = s_rs[ml];
 #pragma unroll
         for (int j = 0; j < 8; ++j) h[j] = h[j] * r * w8[j];
-        *reinterpret_cast<uint4*>(p.normed_out + (int64_t)m * p.N + n0 + c * 8) = f32_to_bf16x8(h);
+        *reinterpret_cast<uint4*>(p.normed_out + (int64_t)(r0 + ml) * p.N + n0 + c * 8) = f32_to_bf16x8(h);
       }
     }
   }
@@ -452,7 +456,7 @@ rowpar_fused_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 // Layout of the caller's workspace (zero-initialised once, left clean by every call);
 // only a single-rank call uses it, for what a multi-rank world keeps in its staging:
 //   [0, 64K)      flag block
-//   [64K, 320K)   row sums [unit][M]
+//   [64K, 320K)   row sums [batch row][tile]
 // All offsets are fixed, so calls of different shapes may share one workspace.
 constexpr size_t kFusedRowsqBytes = (size_t)kMaxFusedTiles * 256 * sizeof(float);
 
@@ -494,9 +498,11 @@ static int fused_plan(FusedPlan* fp, const void* X, const void* W, int64_t M, in
   const int T = fp->g.n_tiles;
   const size_t pipe_bytes = fp->g.smem_bytes - 1024;
   auto fits = [&](int s) {
-    const size_t fw = kTileN / s;
-    const size_t recv = (size_t)(s - 1) * fp->g.m_pad * fw * sizeof(float);
-    const size_t unit = (size_t)M * fw * 2;
+    // a partner owns m_pad / s batch rows, exchanged four at a time
+    if (fp->g.m_pad % (4 * s) != 0) return false;
+    const size_t cw = (size_t)fp->g.m_pad / s;
+    const size_t recv = (size_t)(s - 1) * cw * kTileN * sizeof(float);
+    const size_t unit = cw * kTileN * 2;
     // units are capped by the flag arrays; a cluster leaves a little slack in the
     // co-residency bound because its CTAs must land in one GPC
     return recv + unit <= pipe_bytes && T * s <= kMaxFusedTiles && T * s <= fp->capacity - (s > 1 ? 8 : 0);
@@ -540,7 +546,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   int rc = fused_plan(&fp, X, W, M, N, K_local, device);
   if (rc) return rc;
   const int R = w ? w->ws : 1;
-  const int T = fp.g.n_tiles, S = fp.splits, U = T * S, FW = kTileN / S;
+  const int T = fp.g.n_tiles, S = fp.splits, U = T * S;
   FusedParams p;
   memset(&p, 0, sizeof(p));
   p.M = (int)M; p.N = (int)N; p.m_pad = fp.g.m_pad; p.splits = S; p.stages = fp.g.stages;
@@ -552,7 +558,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   p.normed_out = (__nv_bfloat16*)normed_out;
   p.norm_w = (const __nv_bfloat16*)norm_w;
   uint8_t* wsb = (uint8_t*)workspace;
-  p.tile_bytes = (int64_t)M * FW * 2;  // one unit: [M][FW] bf16
+  p.tile_bytes = (int64_t)(fp.g.m_pad / S) * kTileN * 2;  // one unit: [m_pad / S batch rows][128] bf16
   bool two = false;
   if (R > 1) {
     two = algo == HB_ALGO_TWO_SHOT || (algo == HB_ALGO_AUTO && R > 2 && (size_t)M * N * 2 >= 256 * 1024);
@@ -563,7 +569,7 @@ int rowpar_fused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out
   const size_t part_area = (size_t)R * p.tiles_own * p.tile_bytes;
   p.gather_off = (int64_t)align_up(part_area, 256);
   p.rowsq_off = p.gather_off + (int64_t)align_up(two ? (size_t)U * p.tile_bytes : 0, 256);
-  const size_t need = (size_t)p.rowsq_off + (size_t)((U + 3) & ~3) * M * sizeof(float);
+  const size_t need = (size_t)p.rowsq_off + (size_t)((T + 3) & ~3) * fp.g.m_pad * sizeof(float);
   if (R > 1) {
     if (need > w->staging_bytes)
       return fail(HB_ERR_INVALID_ARG, "fused row-parallel: needs %zu bytes of staging, world has %zu", need,
