@@ -31,6 +31,10 @@ LLAMA_8B = dict(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
 LLAMA_70B = dict(hidden_size=8192, intermediate_size=28672, num_hidden_layers=80, num_attention_heads=64,
                  num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0)
 
+MIXTRAL_8X7B = dict(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                    num_key_value_heads=8, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=1000000.0,
+                    num_local_experts=8, num_experts_per_tok=2, sliding_window=4096)
+
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 
@@ -42,6 +46,9 @@ def workload_for(n_gpus: int, args) -> dict:
     else:
         w = dict(name=f"llama-3.1-70b-shape tp{n_gpus} b128 prompt1024 greedy-decode", shape=dict(LLAMA_70B),
                  batch=128, prompt_len=1024, norm_ones=True)
+    if args.workload == "mixtral":  # the sparse-MoE configuration: 64 sequences, 512-token prompts
+        w = dict(name=f"mixtral-8x7b-shape tp{n_gpus} b64 prompt512 greedy-decode", shape=dict(MIXTRAL_8X7B),
+                 batch=64, prompt_len=512, norm_ones=True)
     if args.layers:
         w["shape"]["num_hidden_layers"] = args.layers
         w["name"] += f" layers{args.layers}"
@@ -319,7 +326,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "kernel_ms_per_step": prof,
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.workload == "auto":
             threads = os.cpu_count() or 1
             line["cpu_baseline"] = cpu_reference_tok_s(shape, P, 4, threads)
         print(json.dumps(line), flush=True)
@@ -345,6 +352,8 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--profile-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="auto", choices=["auto", "mixtral"],
+                    help="auto: Llama-3.1-8B shape on one GPU, 70B shape on several; mixtral: Mixtral-8x7B shape")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

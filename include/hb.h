@@ -126,6 +126,24 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
                               const int32_t* ctx_lens, int64_t n_seqs, int n_q_heads,
                               int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
                               int64_t num_blocks, int n_splits, void* workspace, hb_dtype dtype);
+/* The same with a sliding window (sliding_causal_mask, src/engine/arch/mixtral.rs:155-176):
+ * the query at position ctx-1 attends to the keys ki with ctx-1-ki < sliding_window;
+ * 0 = no window.  Blocks wholly outside the window are not read. */
+int hb_paged_decode_attention_window(void* stream, void* out, const void* q, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables,
+                                     const int32_t* ctx_lens, int64_t n_seqs, int n_q_heads,
+                                     int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
+                                     int64_t num_blocks, int n_splits, void* workspace,
+                                     int sliding_window, hb_dtype dtype);
+
+/* Router of the sparse mixture-of-experts block (SparseMoeBlock::forward,
+ * src/engine/arch/mixtral.rs:371-412): logits = x . w_gate^T (rounded to dtype), softmax over
+ * the experts (rounded to dtype), top_k by descending probability (ties: lower index),
+ * weights renormalised by their sum floored at 1e-9.  scale (device f32 [n_tokens,
+ * n_experts]) receives the weight of each chosen expert and 0 for the others.
+ * x [n_tokens, hidden], w_gate [n_experts, hidden]; n_experts <= 64. */
+int hb_moe_route(void* stream, float* scale, const void* x, const void* w_gate, int64_t n_tokens,
+                 int64_t hidden, int n_experts, int top_k, hb_dtype dtype);
 
 /* The same split-KV decode attention for callers that must not allocate device memory
  * — a host that runs inside a captured or pre-planned memory budget, an embedding
@@ -320,12 +338,18 @@ typedef struct hb_model_shape {
   int64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads,
       num_key_value_heads, vocab_size;
   double rms_norm_eps, rope_theta;
+  /* mixture of experts (src/engine/arch/mixtral.rs:40-57); all 0 for a dense Llama */
+  int64_t num_local_experts;    /* experts per layer, each a SwiGLU FFN of intermediate_size */
+  int64_t num_experts_per_tok;  /* top-k of the router */
+  int64_t sliding_window;       /* attention window in tokens, 0 = none */
 } hb_model_shape;
 
 typedef struct hb_engine hb_engine;
 typedef struct hb_seq hb_seq;
 
-/* Engine::load (src/engine/loader.rs:66-192) for model_type "llama"/"mistral":
+/* Engine::load (src/engine/loader.rs:66-192) for model_type "llama"/"mistral" and
+ * "mixtral" (MixtralBackend::load, src/engine/arch/mixtral.rs:455-516, here also tensor-parallel:
+ * every expert's w1/w3 column-parallel and w2 row-parallel over its intermediate size):
  * reads config.json and the sorted *.safetensors, checks the divisibility rules of
  * TpLlamaBackend::load (src/engine/arch/llama_tp.rs:407-427), shards per
  * src/parallel/shard.rs and uploads this rank's slices.  `world` may be NULL for

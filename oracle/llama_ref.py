@@ -232,7 +232,11 @@ def write_model(path: str, cfg: LlamaTpConfig, weights: dict, model_type: str = 
                 rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta)
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(conf, f)
-    # safetensors layout: u64 header length, JSON header, raw little-endian data
+    write_safetensors(os.path.join(path, "model.safetensors"), weights)
+
+
+def write_safetensors(file_path: str, weights: dict) -> None:
+    """One F32 safetensors file: u64 header length, JSON header, raw little-endian data."""
     header, blobs, off = {}, [], 0
     for name in sorted(weights):
         a = np.ascontiguousarray(weights[name], dtype=np.float32)
@@ -241,7 +245,7 @@ def write_model(path: str, cfg: LlamaTpConfig, weights: dict, model_type: str = 
         off += a.nbytes
     hjson = json.dumps(header, separators=(",", ":")).encode()
     hjson += b" " * ((8 - len(hjson) % 8) % 8)
-    with open(os.path.join(path, "model.safetensors"), "wb") as f:
+    with open(file_path, "wb") as f:
         f.write(len(hjson).to_bytes(8, "little"))
         f.write(hjson)
         for b in blobs:

@@ -1,0 +1,131 @@
+"""Sparse mixture-of-experts decode path (Mixtral, src/engine/arch/mixtral.rs) against the
+CPU oracle on identical seeded inputs: router weights, sliding-window attention, and the
+whole engine (fp32 through the CUDA-core kernels, bf16 through the tcgen05 GEMMs with the
+experts' weights concatenated)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kernels_ref as K
+from oracle import mixtral_ref as M
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, want):
+    return float(np.max(np.abs(got - want))) / max(float(np.max(np.abs(want))), 1e-30)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("n_tokens,hidden,n_experts,top_k", [(7, 256, 8, 2), (64, 4096, 8, 2), (3, 100, 5, 3)])
+def test_moe_route(hb, cuda, dtype, n_tokens, hidden, n_experts, top_k):
+    rng = np.random.default_rng(5)
+    x = K.rnd(rng.standard_normal((n_tokens, hidden), dtype=np.float32), dtype)
+    wg = K.rnd(rng.standard_normal((n_experts, hidden), dtype=np.float32) * 0.05, dtype)
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    got = hb.moe_route(torch.from_numpy(x).to(cuda, tdt), torch.from_numpy(wg).to(cuda, tdt), top_k).cpu().numpy()
+    logits = K.rnd(x @ wg.T, dtype)
+    probs = K.rnd(K.softmax_last(logits.astype(np.float64)).astype(np.float32), dtype)
+    want = np.zeros((n_tokens, n_experts), dtype=np.float32)
+    for t in range(n_tokens):
+        for e, w in M.route(probs[t], top_k):
+            want[t, e] = w
+    # same experts chosen unless two probabilities are within rounding of each other
+    same = (got > 0) == (want > 0)
+    assert same.all(axis=1).mean() >= 0.95
+    rows = same.all(axis=1)
+    assert np.allclose(got[rows], want[rows], atol=2e-2 if dtype == "bf16" else 1e-5)
+    assert np.allclose(got.sum(1), 1.0, atol=1e-5) and ((got > 0).sum(1) == top_k).all()
+
+
+def numpy_window_attention(q, kc, vc, tables, ctx, window):
+    n_seqs, hq, d = q.shape
+    hkv = kc.shape[1]
+    out = np.zeros_like(q)
+    for s in range(n_seqs):
+        n = int(ctx[s])
+        first = max(0, n - window) if window > 0 else 0
+        toks = np.arange(first, n)
+        blk, off = tables[s][toks // 16], toks % 16
+        for h in range(hq):
+            k = kc[blk, h // (hq // hkv), off]      # [n_keys, d]
+            v = vc[blk, h // (hq // hkv), off]
+            sc = (k @ q[s, h]) / np.sqrt(d)
+            p = np.exp(sc - sc.max())
+            out[s, h] = (p / p.sum()) @ v
+    return out
+
+
+@pytest.mark.parametrize("dtype,hd,hq,hkv", [("bf16", 128, 8, 2), ("f32", 64, 4, 2), ("bf16", 128, 8, 1)])
+@pytest.mark.parametrize("window,n_splits", [(24, 1), (40, 3), (1, 1), (1000, 2)])
+def test_sliding_window_attention(hb, cuda, dtype, hd, hq, hkv, window, n_splits):
+    rng = np.random.default_rng(7)
+    n_seqs, num_blocks, max_blocks = 5, 64, 8
+    ctx = np.array([1, 16, 23, 57, 128], dtype=np.int32)
+    q = K.rnd(rng.standard_normal((n_seqs, hq, hd), dtype=np.float32), dtype)
+    kc = K.rnd(rng.standard_normal((num_blocks, hkv, 16, hd), dtype=np.float32), dtype)
+    vc = K.rnd(rng.standard_normal((num_blocks, hkv, 16, hd), dtype=np.float32), dtype)
+    tables = np.stack([rng.permutation(num_blocks)[:max_blocks] for _ in range(n_seqs)]).astype(np.int32)
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    dev = lambda a, t=tdt: torch.from_numpy(a).to(cuda, t)
+    got = hb.paged_decode_attention(dev(q), dev(kc), dev(vc), dev(tables, torch.int32), dev(ctx, torch.int32),
+                                    n_splits=n_splits, sliding_window=window).float().cpu().numpy()
+    want = numpy_window_attention(q, kc, vc, tables, ctx, window)
+    assert rel_err(got, want) <= (2e-2 if dtype == "bf16" else 1e-3)
+
+
+def test_tiny_mixtral_fp32_engine(hb, cuda, tmp_path):
+    """A tiny fp32 Mixtral written as safetensors + config.json: prompts longer than the
+    sliding window, logits of the prefill and of teacher-forced decode steps."""
+    cfg = M.TINY_MIXTRAL
+    weights = M.random_weights(cfg, seed=1, std=0.05, norm_ones=True)
+    M.write_model(str(tmp_path), cfg, weights)
+    eng = hb.Engine.load(str(tmp_path), max_seq_len=96, bf16=False, force_f32=True, max_batch=4)
+    oracle = M.MixtralOracle(cfg, weights, world_size=1, dtype="f32")
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(2, 40)).astype(np.uint32)
+    agree = total = 0
+    for p in prompts:
+        cache = oracle.new_cache()
+        seq = eng.create_kv_cache()
+        want = oracle.forward(p.tolist(), 0, cache)
+        got = eng.forward_with_cache(p, 0, seq)
+        assert rel_err(got, want) <= 1e-3
+        tok = int(np.argmax(want))
+        for step in range(4):
+            pos = len(p) + step
+            want = oracle.forward([tok], pos, cache)
+            got = eng.forward_with_cache([tok], pos, seq)
+            assert rel_err(got, want) <= 1e-3
+            agree += int(np.argmax(got) == np.argmax(want))
+            total += 1
+            tok = int(np.argmax(want))
+        seq.free()
+    assert agree == total
+    eng.close()
+
+
+SHAPE_MOE_TC = dict(hidden_size=512, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=1024, rms_norm_eps=1e-5, rope_theta=1e6,
+                    num_local_experts=4, num_experts_per_tok=2, sliding_window=4096)
+
+
+def test_mixtral_bf16_tensor_core_engine(hb, cuda):
+    """Device-initialised bf16 Mixtral on the tcgen05 path (gate|up of all experts as one
+    SwiGLU GEMM, their down projections as one GEMM over the concatenated K); the oracle
+    runs on the weights read back from the device (expert w2 is a column block)."""
+    eng = hb.Engine.create_random(SHAPE_MOE_TC, seed=2, std=0.05, norm_ones=True, max_seq_len=64, bf16=True,
+                                  max_batch=8)
+    cfg = M.MixtralConfig(**SHAPE_MOE_TC)
+    weights = {name: eng.get_tensor(name).reshape(shape) for name, shape in M.tensor_shapes(cfg).items()}
+    w2 = weights["model.layers.1.block_sparse_moe.experts.3.w2.weight"]
+    assert abs(float(w2.std()) - 0.05) < 5e-3
+    oracle = M.MixtralOracle(cfg, weights, world_size=1, dtype="bf16")
+    B, plen = 8, 12
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, plen)).astype(np.uint32)
+    seqs = [eng.create_kv_cache() for _ in range(B)]
+    logits = np.empty((B, cfg.vocab_size), dtype=np.float32)
+    for t in range(plen):
+        eng.decode_batch(seqs, prompts[:, t], logits=logits)
+    want = np.stack([oracle.forward(prompts[i].tolist(), 0, oracle.new_cache()) for i in range(B)])
+    assert rel_err(logits, want) <= 3e-2
+    eng.close()

@@ -75,6 +75,9 @@ class ModelShape(C.Structure):
         ("vocab_size", C.c_int64),
         ("rms_norm_eps", C.c_double),
         ("rope_theta", C.c_double),
+        ("num_local_experts", C.c_int64),
+        ("num_experts_per_tok", C.c_int64),
+        ("sliding_window", C.c_int64),
     ]
 
 
@@ -93,6 +96,8 @@ _SIGS = {
     "hb_kv_assign_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i]),
     "hb_attention_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "hb_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _vp, _i]),
+    "hb_paged_decode_attention_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _vp, _i, _i]),
+    "hb_moe_route": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _i]),
     "hb_paged_decode_attention_static_max_bytes": (_sz, []),
     "hb_paged_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i, _i]),
     "hb_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
@@ -298,8 +303,10 @@ class kernels:
                                          dtype_code(k.dtype)))
 
 
-def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, n_splits: int = 1, stream=None):
-    """q [n_seqs,hq,d]; caches [num_blocks,hkv,16,d]; block_tables int32 [n_seqs,max_blocks]."""
+def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, n_splits: int = 1, stream=None,
+                           sliding_window: int = 0):
+    """q [n_seqs,hq,d]; caches [num_blocks,hkv,16,d]; block_tables int32 [n_seqs,max_blocks];
+    sliding_window > 0 limits every query to its last `sliding_window` keys."""
     import torch
 
     n_seqs, hq, d = q.shape
@@ -307,11 +314,29 @@ def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, n_splits
     out = torch.empty_like(q)
     ws_bytes = lib.hb_attention_workspace_bytes(n_seqs, hq, d, n_splits)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+    if sliding_window:
+        check(lib.hb_paged_decode_attention_window(_stream(stream), _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                                   _ptr(block_tables), _ptr(ctx_lens), n_seqs, hq, hkv, d,
+                                                   block_tables.shape[1], num_blocks, n_splits, _ptr(ws),
+                                                   sliding_window, dtype_code(q.dtype)))
+        return out
     check(lib.hb_paged_decode_attention(_stream(stream), _ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache),
                                         _ptr(block_tables), _ptr(ctx_lens), n_seqs, hq, hkv, d,
                                         block_tables.shape[1], num_blocks, n_splits, _ptr(ws),
                                         dtype_code(q.dtype)))
     return out
+
+
+def moe_route(x, w_gate, top_k: int, stream=None):
+    """scale [n_tokens, n_experts] f32: renormalised top-k routing weights, 0 elsewhere."""
+    import torch
+
+    n, hidden = x.shape
+    n_experts = w_gate.shape[0]
+    scale = torch.empty((n, n_experts), dtype=torch.float32, device=x.device)
+    check(lib.hb_moe_route(_stream(stream), _ptr(scale), _ptr(x), _ptr(w_gate), n, hidden, n_experts, top_k,
+                           dtype_code(x.dtype)))
+    return scale
 
 
 def paged_decode_attention_static(q, k_cache, v_cache, block_tables, ctx_lens, n_splits: int = 2, stream=None):
@@ -655,7 +680,9 @@ class Engine:
         cfg = cls._config(None, max_seq_len, bf16, tensor_parallel_size, num_kv_blocks, max_batch, force_f32)
         sh = ModelShape(shape["hidden_size"], shape["intermediate_size"], shape["num_hidden_layers"],
                         shape["num_attention_heads"], shape.get("num_key_value_heads", 0),
-                        shape["vocab_size"], shape.get("rms_norm_eps", 1e-5), shape.get("rope_theta", 10000.0))
+                        shape["vocab_size"], shape.get("rms_norm_eps", 1e-5), shape.get("rope_theta", 10000.0),
+                        shape.get("num_local_experts", 0), shape.get("num_experts_per_tok", 0),
+                        shape.get("sliding_window", 0))
         h = C.c_void_p()
         check(lib.hb_engine_create_random(C.byref(sh), C.byref(cfg), world.handle if world else None,
                                           seed, std, int(norm_ones), C.byref(h)))

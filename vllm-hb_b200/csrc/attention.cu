@@ -52,7 +52,7 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
                   const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
                   const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens,
                   int hq, int hkv, int64_t max_blocks, int64_t num_blocks, int n_splits,
-                  float scale, int64_t q_stride) {
+                  float scale, int64_t q_stride, int window) {
   pdl_trigger();
   constexpr int N = Vec16<T>::N;       // elements per 16-byte vector
   constexpr int LPR = HD / N;          // lanes covering one row
@@ -76,8 +76,11 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
 
   const int ctx = ctx_lens[seq];
   const int nblk = (ctx + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
-  const int bps = (nblk + n_splits - 1) / n_splits;
-  const int b0 = split * bps;
+  // sliding window (src/engine/arch/mixtral.rs:155-176): keys ki with ctx-1-ki < window
+  const int first_tok = window > 0 ? max(0, ctx - window) : 0;
+  const int first_blk = first_tok / HB_BLOCK_SIZE;
+  const int bps = (nblk - first_blk + n_splits - 1) / n_splits;
+  const int b0 = first_blk + split * bps;
   const int b1 = min(nblk, b0 + bps);
 
   // query slices, pre-scaled by 1/sqrt(d)
@@ -138,7 +141,7 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
         if (h < NREP) {
           const int tok_in_blk = p * RPP + grp;
           const int tok = (cb + bi) * HB_BLOCK_SIZE + tok_in_blk;
-          s_p[h][bi * HB_BLOCK_SIZE + tok_in_blk] = tok < ctx ? part[i] : -INFINITY;
+          s_p[h][bi * HB_BLOCK_SIZE + tok_in_blk] = (tok < ctx && tok >= first_tok) ? part[i] : -INFINITY;
         }
       }
     }
@@ -275,12 +278,12 @@ template <typename T, int HD, int NREP>
 static int launch_attn(cudaStream_t st, T* out, float* part_o, float* part_ml, const T* q,
                        const T* kc, const T* vc, const int32_t* bt, const int32_t* cl,
                        int64_t n_seqs, int hq, int hkv, int64_t max_blocks, int64_t num_blocks,
-                       int n_splits, int64_t q_stride) {
+                       int n_splits, int64_t q_stride, int window) {
   dim3 grid((unsigned)n_splits, (unsigned)hkv, (unsigned)n_seqs);
   const float scale = 1.0f / sqrtf((float)HD);
   paged_attn_kernel<T, HD, NREP><<<grid, kAttnThreads, 0, st>>>(
       out, part_o, part_ml, q, kc, vc, bt, cl, hq, hkv, max_blocks, num_blocks, n_splits, scale,
-      q_stride);
+      q_stride, window);
   HB_LAUNCH_CHECK();
   if (n_splits > 1) {
     attn_merge_kernel<T><<<(unsigned)(n_seqs * hq), HD <= 64 ? 64 : 128, 0, st>>>(
@@ -293,12 +296,12 @@ static int launch_attn(cudaStream_t st, T* out, float* part_o, float* part_ml, c
 template <typename T, int HD>
 static int dispatch_nrep(int nrep, cudaStream_t st, T* out, float* po, float* pml, const T* q,
                          const T* kc, const T* vc, const int32_t* bt, const int32_t* cl,
-                         int64_t n_seqs, int hq, int hkv, int64_t mb, int64_t nb, int ns, int64_t qs) {
+                         int64_t n_seqs, int hq, int hkv, int64_t mb, int64_t nb, int ns, int64_t qs, int win) {
   switch (nrep) {
-    case 1: return launch_attn<T, HD, 1>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs);
-    case 2: return launch_attn<T, HD, 2>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs);
-    case 4: return launch_attn<T, HD, 4>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs);
-    case 8: return launch_attn<T, HD, 8>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs);
+    case 1: return launch_attn<T, HD, 1>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs, win);
+    case 2: return launch_attn<T, HD, 2>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs, win);
+    case 4: return launch_attn<T, HD, 4>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs, win);
+    case 8: return launch_attn<T, HD, 8>(st, out, po, pml, q, kc, vc, bt, cl, n_seqs, hq, hkv, mb, nb, ns, qs, win);
     default:
       return fail(HB_ERR_INVALID_ARG,
                   "hb_paged_decode_attention: n_q_heads/n_kv_heads = %d not in {1,2,4,8}", nrep);
@@ -311,7 +314,7 @@ bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* 
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int* err_flag);
+                        int64_t num_blocks, int n_splits, int window, int* err_flag);
 
 // Internal entry: q rows may sit inside a wider [q|k|v] projection buffer.  err_flag
 // (device int, may be null) is raised when a bounded wait of the tensor-core kernel ran out.
@@ -319,7 +322,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag) {
+                    hb_dtype dtype, int* err_flag, int window) {
   if (n_seqs == 0) return HB_OK;
   const int nrep = n_q_heads / n_kv_heads;
   float* po = (float*)workspace;
@@ -328,7 +331,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
   if (!force_simt && paged_attention_mma_supported(q, q_stride, k_cache, v_cache, nrep, head_dim, num_blocks,
                                                    n_kv_heads, dtype)) {
     int rc = paged_attention_mma(st, out, po, pml, q, q_stride, k_cache, v_cache, block_tables, ctx_lens, n_seqs,
-                                 n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, err_flag);
+                                 n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, window, err_flag);
     if (rc) return rc;
     if (n_splits > 1) {
       attn_merge_kernel<__nv_bfloat16><<<(unsigned)(n_seqs * n_q_heads), 128, 0, st>>>(
@@ -341,11 +344,11 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
     if (head_dim == 128)
       return (dispatch_nrep<T, 128>(nrep, st, (T*)out, po, pml, (const T*)q, (const T*)k_cache,
                                     (const T*)v_cache, block_tables, ctx_lens, n_seqs, n_q_heads,
-                                    n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, q_stride));
+                                    n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, q_stride, window));
     if (head_dim == 64)
       return (dispatch_nrep<T, 64>(nrep, st, (T*)out, po, pml, (const T*)q, (const T*)k_cache,
                                    (const T*)v_cache, block_tables, ctx_lens, n_seqs, n_q_heads,
-                                   n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, q_stride));
+                                   n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, q_stride, window));
     return fail(HB_ERR_INVALID_ARG, "paged attention: head_dim %d not in {64,128}", head_dim);
   });
   return HB_OK;
@@ -376,7 +379,28 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
   HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention: bad block counts");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads,
-                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr);
+                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, 0);
+}
+
+int hb_paged_decode_attention_window(void* stream, void* out, const void* q, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_tables,
+                                     const int32_t* ctx_lens, int64_t n_seqs, int n_q_heads,
+                                     int n_kv_heads, int head_dim, int64_t max_blocks_per_seq,
+                                     int64_t num_blocks, int n_splits, void* workspace, int sliding_window,
+                                     hb_dtype dtype) {
+  HB_CHECK_ARG(out && q && k_cache && v_cache && block_tables && ctx_lens,
+               "hb_paged_decode_attention_window: null pointer");
+  HB_CHECK_ARG(n_seqs >= 0 && n_seqs <= 65535, "hb_paged_decode_attention_window: n_seqs %lld out of range",
+               (long long)n_seqs);
+  HB_CHECK_ARG(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0,
+               "hb_paged_decode_attention_window: n_q_heads must be a multiple of n_kv_heads");
+  HB_CHECK_ARG(n_splits >= 1 && n_splits <= 64, "hb_paged_decode_attention_window: n_splits out of range");
+  HB_CHECK_ARG(n_splits == 1 || workspace, "hb_paged_decode_attention_window: workspace needed for splits");
+  HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention_window: bad block counts");
+  HB_CHECK_ARG(sliding_window >= 0, "hb_paged_decode_attention_window: negative window");
+  return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
+                             v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
+                             max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, sliding_window);
 }
 
 }  // extern "C"
@@ -441,7 +465,7 @@ int hb_paged_decode_attention_static(void* stream, void* out, const void* q, con
   if (rc) return rc;
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache, v_cache,
                              block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr);
+                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr, 0);
 }
 
 }  // extern "C"

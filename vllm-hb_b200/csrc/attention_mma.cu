@@ -68,7 +68,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                       float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ q,
                       const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens, int hq,
                       int hkv, int nrep, int64_t max_blocks, int64_t num_blocks, int n_splits, float scale,
-                      int64_t q_stride, int* err_flag) {
+                      int64_t q_stride, int window, int* err_flag) {
   constexpr int kMmaAttnWarps = NW, kMmaAttnThreads = NW * 32;
   pdl_trigger();
   pdl_grid_wait();
@@ -83,8 +83,12 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
   const int ctx = ctx_lens[seq];
   const int nblk = (ctx + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
-  const int bps = (nblk + n_splits - 1) / n_splits;
-  const int b0 = split * bps;
+  // sliding window (src/engine/arch/mixtral.rs:155-176): the query at position ctx-1 sees
+  // the keys ki with ctx-1-ki < window
+  const int first_tok = window > 0 ? max(0, ctx - window) : 0;
+  const int first_blk = first_tok / HB_BLOCK_SIZE;
+  const int bps = (nblk - first_blk + n_splits - 1) / n_splits;
+  const int b0 = first_blk + split * bps;
   const int b1 = min(nblk, b0 + bps);
   // this warp's blocks: b0 + warp + NW i, i < n_w
   const int n_w = (b1 - b0 - warp + kMmaAttnWarps - 1) > 0 ? (b1 - b0 - warp + kMmaAttnWarps - 1) / kMmaAttnWarps : 0;
@@ -200,7 +204,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int tok = tok0 + nt * 8 + 2 * t + (e & 1);
-        const float v = tok < ctx ? sc[nt][e] * scale : -INFINITY;
+        const float v = (tok < ctx && tok >= first_tok) ? sc[nt][e] * scale : -INFINITY;
         sc[nt][e] = v;
         if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
@@ -376,7 +380,7 @@ int paged_attention_mma_prepare() {
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int* err_flag) {
+                        int64_t num_blocks, int n_splits, int window, int* err_flag) {
   int rc = paged_attention_mma_prepare();
   if (rc) return rc;
   CUtensorMap tm_k, tm_v;
@@ -400,11 +404,11 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
   if (nw == 2) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag));
   } else {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<4>, grid, dim3(128), mma_attn_smem(4), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, err_flag));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag));
   }
   return HB_OK;
 }

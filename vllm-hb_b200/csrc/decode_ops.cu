@@ -105,7 +105,7 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
 
 template <typename T>
 __global__ void fill_normal_kernel(T* __restrict__ dst, int64_t rows, int64_t cols, int64_t row0,
-                                   int64_t col0, int64_t g_cols, uint64_t key, float std) {
+                                   int64_t col0, int64_t g_cols, uint64_t key, float std, int64_t dst_ld) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * cols) return;
   const int64_t r = idx / cols, c = idx % cols;
@@ -114,7 +114,7 @@ __global__ void fill_normal_kernel(T* __restrict__ dst, int64_t rows, int64_t co
   const float u1 = ((float)(z >> 40) + 1.0f) * (1.0f / 16777216.0f);        // (0, 1]
   const float u2 = ((float)((z >> 16) & 0xFFFFFF) + 0.5f) * (1.0f / 16777216.0f);
   const float n = sqrtf(-2.0f * __logf(u1)) * __cosf(6.28318530717958647692f * u2);
-  dst[idx] = from_f32<T>(n * std);
+  dst[r * dst_ld + c] = from_f32<T>(n * std);
 }
 
 template <typename T>
@@ -124,20 +124,22 @@ __global__ void fill_const_kernel(T* __restrict__ dst, int64_t n, float v) {
 }
 
 template <typename T>
-__global__ void to_f32_kernel(float* __restrict__ dst, const T* __restrict__ src, int64_t n) {
+__global__ void to_f32_kernel(float* __restrict__ dst, const T* __restrict__ src, int64_t n, int64_t cols,
+                              int64_t src_ld) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx < n) dst[idx] = to_f32<T>(src[idx]);
+  if (idx < n) dst[idx] = to_f32<T>(src[(idx / cols) * src_ld + idx % cols]);
 }
 
 int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
                 int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
-                float std) {
+                float std, int64_t dst_ld) {
   const int64_t n = rows * cols;
+  if (dst_ld <= 0) dst_ld = cols;
   if (n == 0) return HB_OK;
   const uint64_t key = seed * 0xD1342543DE82EF95ull + tensor_id * 0x9E3779B97F4A7C15ull + 1;
   HB_DISPATCH_DTYPE(dtype, T, {
     fill_normal_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((T*)dst, rows, cols, row0,
-                                                                      col0, g_cols, key, std);
+                                                                      col0, g_cols, key, std, dst_ld);
   });
   HB_LAUNCH_CHECK();
   return HB_OK;
@@ -152,10 +154,12 @@ int fill_const(cudaStream_t st, void* dst, hb_dtype dtype, int64_t n, float valu
   return HB_OK;
 }
 
-int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n) {
+int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n, int64_t cols, int64_t src_ld) {
   if (n == 0) return HB_OK;
+  if (cols <= 0) cols = n;
+  if (src_ld <= 0) src_ld = cols;
   HB_DISPATCH_DTYPE(dtype, T, {
-    to_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, (const T*)src, n);
+    to_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, (const T*)src, n, cols, src_ld);
   });
   HB_LAUNCH_CHECK();
   return HB_OK;

@@ -37,8 +37,11 @@ namespace hb {
 struct LayerWeights {
   void* wqkv = nullptr;   // [(hq_l + 2*hkv_l) * hd, H]   rows: q | k | v (column-parallel)
   void* wo = nullptr;     // [H, hq_l * hd]               (row-parallel)
-  void* wgu = nullptr;    // [2 * I_l, H]                 rows: gate | up (column-parallel)
-  void* wdown = nullptr;  // [H, I_l]                     (row-parallel)
+  // Dense FFN: E = 1.  Mixture of experts: the experts' weights are concatenated, gate
+  // (w1) rows of all experts first, then their up (w3) rows; down (w2) along K.
+  void* wgu = nullptr;    // [2 * E * I_l, H]             rows: gate_0..gate_{E-1} | up_0..up_{E-1}
+  void* wdown = nullptr;  // [H, E * I_l]                 columns: expert e at [e * I_l, (e+1) * I_l)
+  void* wgate = nullptr;  // [E, H] router (replicated), null for a dense FFN
   void* norm_in = nullptr;
   void* norm_post = nullptr;
 };
@@ -46,6 +49,7 @@ struct LayerWeights {
 struct NamedTensor {
   void* ptr;
   int64_t rows, cols;
+  int64_t ld = 0;  // row stride in elements (0 = cols): expert down-projections are column blocks
 };
 
 enum GemmKind { kQkv = 0, kO = 1, kGateUp = 2, kDown = 3, kLmHead = 4 };
@@ -71,6 +75,10 @@ struct hb_engine {
   int64_t H = 0, I = 0, L = 0, hq = 0, hkv = 0, hd = 0, V = 0;
   double eps = 1e-5, theta = 10000.0;
   int64_t hq_l = 0, hkv_l = 0, I_l = 0, qkv_rows = 0;
+  // mixture of experts (mixtral.rs:40-57): E experts, top-k routing, sliding window; I_e = E * I_l
+  int64_t E = 1, topk = 1, window = 0, I_e = 0;
+  bool moe = false;
+  float* d_scale = nullptr;  // [max_batch, E] routing weights of the step
   // weights
   void* embed = nullptr;
   void* lm_head = nullptr;
@@ -144,8 +152,9 @@ static bool same_dtype(const std::string& s, hb_dtype d) {
 // Copy rows [r0, r0+nr) x cols [c0, c0+nc) of a host [rows, cols] tensor to device
 // memory at dst (row-major [nr, nc]) converting to the engine dtype — the narrow() of
 // column_shard / row_shard (src/parallel/shard.rs:46-74) followed by to_device.
+// dst_ld: row stride of the destination in elements (0 = nc, contiguous)
 static int upload_slice(hb_engine* e, void* dst, const StTensor& t, int64_t cols, int64_t r0,
-                        int64_t nr, int64_t c0, int64_t nc, std::vector<uint8_t>* scratch) {
+                        int64_t nr, int64_t c0, int64_t nc, std::vector<uint8_t>* scratch, int64_t dst_ld = 0) {
   scratch->resize((size_t)nr * nc * e->es);
   uint8_t* s = scratch->data();
   if (same_dtype(t.dtype, e->dtype)) {
@@ -155,6 +164,11 @@ static int upload_slice(hb_engine* e, void* dst, const StTensor& t, int64_t cols
     for (int64_t r = 0; r < nr; ++r)
       for (int64_t c = 0; c < nc; ++c)
         f32_to_dst(s, e->dtype, r * nc + c, src_to_f32(t.data, t.dtype, (r0 + r) * cols + c0 + c));
+  }
+  if (dst_ld > 0 && dst_ld != nc) {
+    HB_CUDA_CHECK(cudaMemcpy2D(dst, (size_t)dst_ld * e->es, s, (size_t)nc * e->es, (size_t)nc * e->es, (size_t)nr,
+                               cudaMemcpyHostToDevice));
+    return HB_OK;
   }
   HB_CUDA_CHECK(cudaMemcpy(dst, s, scratch->size(), cudaMemcpyHostToDevice));
   return HB_OK;
@@ -211,11 +225,19 @@ static int setup_shape(hb_engine* e, const hb_model_shape& s) {
   int rc = check_divisibility(e);
   if (rc) return rc;
   e->hq_l = e->hq / e->ws; e->hkv_l = e->hkv / e->ws; e->I_l = e->I / e->ws;
+  e->moe = s.num_local_experts > 0;
+  e->E = e->moe ? s.num_local_experts : 1;
+  e->topk = e->moe ? (s.num_experts_per_tok > 0 ? s.num_experts_per_tok : 2) : 1;
+  e->window = s.sliding_window > 0 ? s.sliding_window : 0;
+  if (e->E > 64) return fail(HB_ERR_INVALID_ARG, "num_local_experts %lld unsupported (<= 64)", (long long)e->E);
+  e->I_e = e->E * e->I_l;
   e->qkv_rows = (e->hq_l + 2 * e->hkv_l) * e->hd;
   const char* g = getenv("HB_GEMM");
   const bool want_simt = g && std::string(g) == "simt";
   e->use_tc = !want_simt && e->dtype == HB_BF16 && e->H % 64 == 0 && (e->hq_l * e->hd) % 64 == 0 &&
               e->I_l % 64 == 0;
+  // expert boundaries must fall on 128-feature tiles of the SwiGLU GEMM
+  if (e->moe && e->I_l % 128 != 0) e->use_tc = false;
   return HB_OK;
 }
 
@@ -229,8 +251,9 @@ static int alloc_weights(hb_engine* e) {
   for (auto& l : e->layers) {
     if ((rc = dev_alloc(e, &l.wqkv, (size_t)e->qkv_rows * e->H * es))) return rc;
     if ((rc = dev_alloc(e, &l.wo, (size_t)e->H * e->hq_l * e->hd * es))) return rc;
-    if ((rc = dev_alloc(e, &l.wgu, (size_t)2 * e->I_l * e->H * es))) return rc;
-    if ((rc = dev_alloc(e, &l.wdown, (size_t)e->H * e->I_l * es))) return rc;
+    if ((rc = dev_alloc(e, &l.wgu, (size_t)2 * e->I_e * e->H * es))) return rc;
+    if ((rc = dev_alloc(e, &l.wdown, (size_t)e->H * e->I_e * es))) return rc;
+    if (e->moe && (rc = dev_alloc(e, &l.wgate, (size_t)e->E * e->H * es))) return rc;
     if ((rc = dev_alloc(e, &l.norm_in, (size_t)e->H * es))) return rc;
     if ((rc = dev_alloc(e, &l.norm_post, (size_t)e->H * es))) return rc;
   }
@@ -247,9 +270,20 @@ static int alloc_weights(hb_engine* e) {
     e->named[pf + ".self_attn.k_proj.weight"] = {qkv + (size_t)e->hq_l * e->hd * rowb, e->hkv_l * e->hd, e->H};
     e->named[pf + ".self_attn.v_proj.weight"] = {qkv + (size_t)(e->hq_l + e->hkv_l) * e->hd * rowb, e->hkv_l * e->hd, e->H};
     e->named[pf + ".self_attn.o_proj.weight"] = {l.wo, e->H, e->hq_l * e->hd};
-    e->named[pf + ".mlp.gate_proj.weight"] = {l.wgu, e->I_l, e->H};
-    e->named[pf + ".mlp.up_proj.weight"] = {(uint8_t*)l.wgu + (size_t)e->I_l * rowb, e->I_l, e->H};
-    e->named[pf + ".mlp.down_proj.weight"] = {l.wdown, e->H, e->I_l};
+    if (!e->moe) {
+      e->named[pf + ".mlp.gate_proj.weight"] = {l.wgu, e->I_l, e->H};
+      e->named[pf + ".mlp.up_proj.weight"] = {(uint8_t*)l.wgu + (size_t)e->I_l * rowb, e->I_l, e->H};
+      e->named[pf + ".mlp.down_proj.weight"] = {l.wdown, e->H, e->I_l};
+    } else {
+      // names of mixtral.rs:330-333,354-363
+      e->named[pf + ".block_sparse_moe.gate.weight"] = {l.wgate, e->E, e->H};
+      for (int64_t x = 0; x < e->E; ++x) {
+        const std::string ex = pf + ".block_sparse_moe.experts." + std::to_string(x);
+        e->named[ex + ".w1.weight"] = {(uint8_t*)l.wgu + (size_t)(x * e->I_l) * rowb, e->I_l, e->H};
+        e->named[ex + ".w3.weight"] = {(uint8_t*)l.wgu + (size_t)(e->I_e + x * e->I_l) * rowb, e->I_l, e->H};
+        e->named[ex + ".w2.weight"] = {(uint8_t*)l.wdown + (size_t)(x * e->I_l) * es, e->H, e->I_l, e->I_e};
+      }
+    }
     e->named[pf + ".input_layernorm.weight"] = {l.norm_in, 1, e->H};
     e->named[pf + ".post_attention_layernorm.weight"] = {l.norm_post, 1, e->H};
   }
@@ -289,8 +323,9 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = dev_alloc(e, &e->d_x, (size_t)B * e->H * es))) return rc;
   if ((rc = dev_alloc(e, &e->d_qkv, (size_t)B * e->qkv_rows * es))) return rc;
   if ((rc = dev_alloc(e, &e->d_attn, (size_t)B * e->hq_l * e->hd * es))) return rc;
-  if ((rc = dev_alloc(e, &e->d_gu, (size_t)B * 2 * e->I_l * es))) return rc;
-  if ((rc = dev_alloc(e, &e->d_act, (size_t)B * e->I_l * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_gu, (size_t)B * 2 * e->I_e * es))) return rc;
+  if ((rc = dev_alloc(e, &e->d_act, (size_t)B * e->I_e * es))) return rc;
+  if (e->moe && (rc = dev_alloc(e, (void**)&e->d_scale, (size_t)B * e->E * 4))) return rc;
   if ((rc = dev_alloc(e, &e->d_proj, (size_t)B * e->H * es))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_logits, (size_t)B * e->V * 4))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_next, (size_t)B * 4))) return rc;
@@ -311,7 +346,7 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   e->use_fused = e->use_tc && ff && ff[0] == '1';
   if (e->use_fused) {
     const size_t fw = std::max(rowpar_fused_workspace_bytes(B, e->H, e->hq_l * e->hd),
-                               rowpar_fused_workspace_bytes(B, e->H, e->I_l));
+                               rowpar_fused_workspace_bytes(B, e->H, e->I_e));
     if (fw == 0) e->use_fused = false;
     else {
       if ((rc = dev_alloc(e, &e->d_fused_ws, fw))) return rc;
@@ -347,11 +382,11 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
       if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kQkv], e->d_x, w.wqkv, B, e->qkv_rows, e->H, kEpiStore, false, e->device))) return rc;
       if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kO], e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, kEpiStore, false, e->device))) return rc;
       if (e->fused_swiglu) {
-        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_l, e->H, kEpiSwiGLU, false, e->device))) return rc;
+        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_e, e->H, kEpiSwiGLU, false, e->device))) return rc;
       } else {
-        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_l, e->H, kEpiStore, false, e->device))) return rc;
+        if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_e, e->H, kEpiStore, false, e->device))) return rc;
       }
-      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_l, kEpiStore, false, e->device))) return rc;
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_e, kEpiStore, false, e->device))) return rc;
       for (int k = 0; k < 4; ++k) ws = std::max(ws, sp.layer[l * 4 + k].workspace_bytes());
     }
     if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
@@ -432,7 +467,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype, e->d_err))) return rc;
+                              e->dtype, e->d_err, (int)e->window))) return rc;
     e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);
@@ -452,25 +487,38 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
       ++e->last_launches;
     }
+    // mixture of experts: routing weights of every token       mixtral.rs:371-412
+    if (e->moe) {
+      prof_mark(e, kCatOther);
+      if ((rc = moe_route(st, e->d_scale, e->d_x, w.wgate, B, e->H, (int)e->E, (int)e->topk, e->dtype))) return rc;
+      ++e->last_launches;
+    }
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
     prof_mark(e, kCatGemmGateUp);
     if (e->use_tc && e->fused_swiglu) {
-      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
+      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false))) return rc;
     } else {
-      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_l, e->H, false))) return rc;
+      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false))) return rc;
       prof_mark(e, kCatOther);
-      if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_l, e->dtype))) return rc;
+      if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_e, e->dtype))) return rc;
+      ++e->last_launches;
+    }
+    if (e->moe) {
+      // every expert ran on every token; the ones a token did not choose get weight 0,
+      // the chosen ones their renormalised probability                 mixtral.rs:404-427
+      prof_mark(e, kCatOther);
+      if ((rc = moe_scale_act(st, e->d_act, e->d_scale, B, e->I_l, (int)e->E, e->dtype))) return rc;
       ++e->last_launches;
     }
     // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
     const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
     prof_mark(e, kCatGemmDown);
-    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->I_l)) {
-      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_l, eps,
+    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->I_e)) {
+      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_e, eps,
                              HB_ALGO_AUTO, e->d_fused_ws))) return rc;
       ++e->last_launches;
     } else {
-      if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_l, false))) return rc;
+      if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
       if (e->ws > 1) {
         prof_mark(e, kCatComm);
         if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
@@ -640,9 +688,23 @@ int hb_engine_create_random(const hb_model_shape* shape, const hb_model_config* 
     if ((rc = hb::fill_normal(st, qkv + (size_t)qr * rowb, g->dtype, kr, g->H, r * kr, 0, g->H, seed, t0 + 1, std))) return rc;
     if ((rc = hb::fill_normal(st, qkv + (size_t)(qr + kr) * rowb, g->dtype, kr, g->H, r * kr, 0, g->H, seed, t0 + 2, std))) return rc;
     if ((rc = hb::fill_normal(st, w.wo, g->dtype, g->H, qr, 0, r * qr, g->hq * g->hd, seed, t0 + 3, std))) return rc;
-    if ((rc = hb::fill_normal(st, w.wgu, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 4, std))) return rc;
-    if ((rc = hb::fill_normal(st, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 5, std))) return rc;
-    if ((rc = hb::fill_normal(st, w.wdown, g->dtype, g->H, g->I_l, 0, r * g->I_l, g->I, seed, t0 + 6, std))) return rc;
+    if (!g->moe) {
+      if ((rc = hb::fill_normal(st, w.wgu, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 4, std))) return rc;
+      if ((rc = hb::fill_normal(st, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, t0 + 5, std))) return rc;
+      if ((rc = hb::fill_normal(st, w.wdown, g->dtype, g->H, g->I_l, 0, r * g->I_l, g->I, seed, t0 + 6, std))) return rc;
+    } else {
+      // tensor ids of expert x: 1024 + 4096*layer + 4*x + {0: w1, 1: w3, 2: w2}; router: t0 + 9
+      if ((rc = hb::fill_normal(st, w.wgate, g->dtype, g->E, g->H, 0, 0, g->H, seed, t0 + 9, std))) return rc;
+      for (int64_t x = 0; x < g->E; ++x) {
+        const uint64_t tx = 1024 + 4096 * (uint64_t)l + 4 * (uint64_t)x;
+        uint8_t* w1 = (uint8_t*)w.wgu + (size_t)(x * g->I_l) * rowb;
+        uint8_t* w3 = (uint8_t*)w.wgu + (size_t)(g->I_e + x * g->I_l) * rowb;
+        uint8_t* w2 = (uint8_t*)w.wdown + (size_t)(x * g->I_l) * g->es;
+        if ((rc = hb::fill_normal(st, w1, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, tx + 0, std))) return rc;
+        if ((rc = hb::fill_normal(st, w3, g->dtype, g->I_l, g->H, r * g->I_l, 0, g->H, seed, tx + 1, std))) return rc;
+        if ((rc = hb::fill_normal(st, w2, g->dtype, g->H, g->I_l, 0, r * g->I_l, g->I, seed, tx + 2, std, g->I_e))) return rc;
+      }
+    }
     if ((rc = fill_norm(w.norm_in, t0 + 7))) return rc;
     if ((rc = fill_norm(w.norm_post, t0 + 8))) return rc;
   }
@@ -665,9 +727,12 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
   hb::JsonParser jp(text.data(), text.size());
   if (!jp.parse(&root, &err)) return hb::fail(HB_ERR_IO, "config.json: %s", err.c_str());
   const std::string mt = root.string_or("model_type", "llama");
-  if (mt != "llama" && mt != "mistral")
-    return hb::fail(HB_ERR_INVALID_ARG, "model_type '%s' is not served by this path (llama, mistral)", mt.c_str());
+  if (mt != "llama" && mt != "mistral" && mt != "mixtral")
+    return hb::fail(HB_ERR_INVALID_ARG, "model_type '%s' is not served by this path (llama, mistral, mixtral)",
+                    mt.c_str());
+  const bool mixtral = mt == "mixtral";
   hb_model_shape sh;
+  memset(&sh, 0, sizeof(sh));
   sh.hidden_size = (int64_t)root.number_or("hidden_size", 0);
   sh.intermediate_size = (int64_t)root.number_or("intermediate_size", 0);
   sh.num_hidden_layers = (int64_t)root.number_or("num_hidden_layers", 0);
@@ -675,7 +740,14 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
   sh.num_key_value_heads = (int64_t)root.number_or("num_key_value_heads", 0);
   sh.vocab_size = (int64_t)root.number_or("vocab_size", 0);
   sh.rms_norm_eps = root.number_or("rms_norm_eps", 1e-5);     // llama_tp.rs:68-70
-  sh.rope_theta = root.number_or("rope_theta", 10000.0);      // llama_tp.rs:71-73
+  sh.rope_theta = root.number_or("rope_theta", mixtral ? 1000000.0 : 10000.0);  // llama_tp.rs:71-73, mixtral.rs:56-58
+  if (mixtral) {  // mixtral.rs:40-57
+    sh.num_local_experts = (int64_t)root.number_or("num_local_experts", 0);
+    sh.num_experts_per_tok = (int64_t)root.number_or("num_experts_per_tok", 0);
+    sh.sliding_window = (int64_t)root.number_or("sliding_window", 4096);
+    if (sh.num_local_experts < 1 || sh.num_experts_per_tok < 1)
+      return hb::fail(HB_ERR_INVALID_ARG, "mixtral config.json needs num_local_experts and num_experts_per_tok");
+  }
   if ((rc = hb::setup_shape(e.get(), sh))) return rc;
   if ((rc = hb::alloc_weights(e.get()))) return rc;
 
@@ -724,12 +796,31 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
     if ((rc = hb::upload_slice(g, qkv + (size_t)(qr + kr) * rowb, *t, g->H, r * kr, kr, 0, g->H, &scratch))) return rc;
     if ((rc = get(pf + ".self_attn.o_proj.weight", g->H, qd, &t))) return rc;
     if ((rc = hb::upload_slice(g, w.wo, *t, qd, 0, g->H, r * qr, qr, &scratch))) return rc;
-    if ((rc = get(pf + ".mlp.gate_proj.weight", g->I, g->H, &t))) return rc;
-    if ((rc = hb::upload_slice(g, w.wgu, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
-    if ((rc = get(pf + ".mlp.up_proj.weight", g->I, g->H, &t))) return rc;
-    if ((rc = hb::upload_slice(g, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
-    if ((rc = get(pf + ".mlp.down_proj.weight", g->H, g->I, &t))) return rc;
-    if ((rc = hb::upload_slice(g, w.wdown, *t, g->I, 0, g->H, r * g->I_l, g->I_l, &scratch))) return rc;
+    if (!g->moe) {
+      if ((rc = get(pf + ".mlp.gate_proj.weight", g->I, g->H, &t))) return rc;
+      if ((rc = hb::upload_slice(g, w.wgu, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+      if ((rc = get(pf + ".mlp.up_proj.weight", g->I, g->H, &t))) return rc;
+      if ((rc = hb::upload_slice(g, (uint8_t*)w.wgu + (size_t)g->I_l * rowb, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+      if ((rc = get(pf + ".mlp.down_proj.weight", g->H, g->I, &t))) return rc;
+      if ((rc = hb::upload_slice(g, w.wdown, *t, g->I, 0, g->H, r * g->I_l, g->I_l, &scratch))) return rc;
+    } else {
+      // mixtral.rs:330-333,354-363: w1 (gate) and w3 (up) column-parallel, w2 (down)
+      // row-parallel over the expert's intermediate size; the router is replicated
+      if ((rc = get(pf + ".block_sparse_moe.gate.weight", g->E, g->H, &t))) return rc;
+      if ((rc = hb::upload_slice(g, w.wgate, *t, g->H, 0, g->E, 0, g->H, &scratch))) return rc;
+      for (int64_t x = 0; x < g->E; ++x) {
+        const std::string ex = pf + ".block_sparse_moe.experts." + std::to_string(x);
+        uint8_t* w1 = (uint8_t*)w.wgu + (size_t)(x * g->I_l) * rowb;
+        uint8_t* w3 = (uint8_t*)w.wgu + (size_t)(g->I_e + x * g->I_l) * rowb;
+        uint8_t* w2 = (uint8_t*)w.wdown + (size_t)(x * g->I_l) * g->es;
+        if ((rc = get(ex + ".w1.weight", g->I, g->H, &t))) return rc;
+        if ((rc = hb::upload_slice(g, w1, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+        if ((rc = get(ex + ".w3.weight", g->I, g->H, &t))) return rc;
+        if ((rc = hb::upload_slice(g, w3, *t, g->H, r * g->I_l, g->I_l, 0, g->H, &scratch))) return rc;
+        if ((rc = get(ex + ".w2.weight", g->H, g->I, &t))) return rc;
+        if ((rc = hb::upload_slice(g, w2, *t, g->I, 0, g->H, r * g->I_l, g->I_l, &scratch, g->I_e))) return rc;
+      }
+    }
     if ((rc = get(pf + ".input_layernorm.weight", 1, g->H, &t))) return rc;
     if ((rc = hb::upload_slice(g, w.norm_in, *t, g->H, 0, 1, 0, g->H, &scratch))) return rc;
     if ((rc = get(pf + ".post_attention_layernorm.weight", 1, g->H, &t))) return rc;
@@ -759,7 +850,7 @@ double hb_engine_step_bytes(const hb_engine* e, const int32_t* ctx_lens, int64_t
   const double es = (double)e->es;
   double w = 0.0;
   w += (double)e->L * ((double)e->qkv_rows * e->H + (double)e->H * e->hq_l * e->hd +
-                       3.0 * (double)e->I_l * e->H + 2.0 * e->H) * es;
+                       3.0 * (double)e->I_e * e->H + (e->moe ? (double)e->E * e->H : 0.0) + 2.0 * e->H) * es;
   w += ((double)e->V * e->H + e->H) * es;    // lm_head + final norm
   w += (double)n_seqs * e->H * es;            // embedding rows
   double kv = 0.0;
@@ -779,7 +870,7 @@ int64_t hb_engine_get_tensor(hb_engine* e, const char* name, float* out, int64_t
   cudaSetDevice(e->device);
   float* tmp = nullptr;
   if (cudaMalloc((void**)&tmp, (size_t)n * 4) != cudaSuccess) return hb::fail(HB_ERR_CUDA, "cudaMalloc failed");
-  int rc = hb::to_f32(e->stream, tmp, it->second.ptr, e->dtype, n);
+  int rc = hb::to_f32(e->stream, tmp, it->second.ptr, e->dtype, n, it->second.cols, it->second.ld);
   if (!rc && cudaMemcpyAsync(out, tmp, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) rc = HB_ERR_CUDA;
   cudaStreamSynchronize(e->stream);
   cudaFree(tmp);
@@ -831,7 +922,7 @@ double hb_engine_gemm_bytes(const hb_engine* e, int64_t B) {
   if (!e) return -1.0;
   const double es = (double)e->es, b = (double)B;
   const double qkv = (double)e->qkv_rows, o_in = (double)e->hq_l * e->hd, H = (double)e->H,
-               Il = (double)e->I_l, V = (double)e->V;
+               Il = (double)e->I_e, V = (double)e->V;
   double per_layer = (qkv * H + b * H + b * qkv) * es        // q|k|v projection
                      + (H * o_in + b * o_in + b * H) * es    // o_proj
                      + (2 * Il * H + b * H + b * Il) * es    // gate|up with the SwiGLU epilogue

@@ -9,10 +9,17 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag = nullptr);
+                    hb_dtype dtype, int* err_flag = nullptr, int window = 0);
 // Opts the tensor-core attention kernel in to its shared memory (once per device,
 // outside any stream capture).
 int paged_attention_mma_prepare();
+
+// Mixture-of-experts routing (moe.cu): scale[m, e] = renormalised top-k softmax weight of
+// expert e for token m, 0 for the others; moe_scale_act multiplies act[m, e*inter + i] by it.
+int moe_route(cudaStream_t st, float* scale, const void* x, const void* w_gate, int64_t n_tokens,
+              int64_t hidden, int n_experts, int top_k, hb_dtype dtype);
+int moe_scale_act(cudaStream_t st, void* act, const float* scale, int64_t n_tokens, int64_t inter,
+                  int n_experts, hb_dtype dtype);
 
 // RoPE on the q and k parts of a fused [q | k | v] projection row and the paged KV
 // write in one pass: q is rotated in place, rotated k and v go straight to their slot.
@@ -25,9 +32,11 @@ int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
 // from a counter-based generator keyed by (seed, tensor id, global element index).
 int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
                 int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
-                float std);
+                float std, int64_t dst_ld = 0);  // dst_ld: row stride of dst in elements (0 = cols)
 int fill_const(cudaStream_t st, void* dst, hb_dtype dtype, int64_t n, float value);
 // dst (f32) = src (dtype)
-int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n);
+// cols / src_ld: the source is [n / cols, cols] with row stride src_ld (0 = contiguous)
+int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n, int64_t cols = 0,
+           int64_t src_ld = 0);
 
 }  // namespace hb
