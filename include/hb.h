@@ -254,6 +254,19 @@ int hb_world_status(hb_world* w);
 int hb_all_reduce(hb_world* w, void* stream, void* buf, size_t count, hb_dtype dtype,
                   hb_algo algo);
 
+/* All-reduce + residual add + RMSNorm in one kernel per rank:
+ *   s = SUM_ranks partial_r (fp32 in rank order, rounded once), resid_out = resid_in + s,
+ *   normed_out = rms_norm(resid_out; norm_w, eps)
+ * — the exchange and the two elementwise steps between a row-parallel projection and the
+ * next layer input (src/engine/arch/llama_tp.rs:533-552 and :563-571,517-522), with the
+ * values of hb_all_reduce followed by hb_add_rms_norm bit for bit.  partial, resid_in,
+ * resid_out, normed_out are [rows, hidden] on this rank (resid_out may alias resid_in;
+ * normed_out may be NULL); rows <= 256, hidden * element size a multiple of 16 bytes and
+ * at most 32 KiB; every rank calls it with the same shapes. */
+int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void* resid_out,
+                               const void* partial, const void* resid_in, const void* norm_w,
+                               int64_t rows, int64_t hidden, float eps, hb_dtype dtype, hb_algo algo);
+
 /* Fused row-parallel projection: normed_out = rms_norm(resid_out),
  * resid_out = resid_in + SUM_ranks( X_r[M,Kl] . W_r[N,Kl]^T ), one kernel per rank:
  * tcgen05 GEMM tiles are pushed to the owning peer's staging over NVLink, reduced

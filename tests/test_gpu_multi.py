@@ -89,6 +89,47 @@ def test_all_reduce_errors(hb, worlds):
             hb.check(hb.lib.hb_all_reduce(w.handle, None, buf.data_ptr(), 8, 7, 0))
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("M,N", [(1, 8192), (7, 4096), (64, 8192), (128, 8192), (256, 1024)])
+@pytest.mark.parametrize("algo", ["auto", "one_shot", "two_shot"])
+def test_all_reduce_add_rms_norm(hb, worlds, dtype, M, N, algo):
+    """One kernel per rank = hb_all_reduce followed by hb_add_rms_norm, bit for bit, on
+    every rank (llama_tp.rs:533-552); two calls in a row reuse the staging area."""
+    R = len(worlds)
+    code = {"one_shot": hb.ALGO_ONE_SHOT, "two_shot": hb.ALGO_TWO_SHOT, "auto": hb.ALGO_AUTO}[algo]
+    tdt = TORCH[dtype]
+    parts = [K.rnd(np.random.default_rng(10 + r).standard_normal((M, N)).astype(np.float32), dtype) for r in range(R)]
+    resid = K.rnd(np.random.default_rng(4).standard_normal((M, N)).astype(np.float32), dtype)
+    nw = K.rnd((1.0 + 0.1 * np.random.default_rng(5).standard_normal(N)).astype(np.float32), dtype)
+
+    def put(a, w):
+        return torch.from_numpy(a).to(f"cuda:{w.device()}", tdt)
+
+    ins = on_all(worlds, lambda r, w: (put(parts[r], w), put(resid, w), put(nw, w)))
+    for rep in range(2):
+        outs = on_all(worlds, lambda r, w: w.all_reduce_add_rms_norm(*ins[r], 1e-5, code))
+        assert all(w.status() == 0 for w in worlds)
+
+        # the separate kernels: every rank launches its all-reduce before any rank waits for it
+        sums = on_all(worlds, lambda r, w: w.all_reduce(ins[r][0].clone(), code))
+
+        def add_norm(r, w):
+            normed, res = torch.empty_like(sums[r]), torch.empty_like(sums[r])
+            hb.check(hb.lib.hb_add_rms_norm(None, normed.data_ptr(), res.data_ptr(), sums[r].data_ptr(),
+                                            ins[r][1].data_ptr(), ins[r][2].data_ptr(), M, N, 1e-5, hb.dtype_code(tdt)))
+            return normed, res
+
+        want = on_all(worlds, add_norm)
+        for r in range(R):
+            assert torch.equal(outs[r][1], want[r][1]) and torch.equal(outs[r][0], want[r][0]), (r, rep)
+        # and against the oracle: sum in rank order in fp32, one rounding, add, norm
+        acc = np.zeros((M, N), dtype=np.float32)
+        for p_ in parts:
+            acc = acc + p_
+        want_h = K.rnd(resid + K.rnd(acc, dtype), dtype)
+        assert float(np.max(np.abs(host(outs[0][1]) - want_h))) <= (1e-5 if dtype == "f32" else 2e-2) * float(np.max(np.abs(want_h)))
+
+
 @pytest.mark.parametrize("M,N,K_", [(1, 8192, 8192), (8, 8192, 28672), (64, 8192, 8192), (128, 8192, 28672), (256, 4096, 4096)])
 @pytest.mark.parametrize("algo", ["auto", "one_shot", "two_shot"])
 def test_fused_rowparallel(hb, worlds, M, N, K_, algo):

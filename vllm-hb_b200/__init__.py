@@ -123,6 +123,7 @@ _SIGS = {
     "hb_world_stream": (_vp, [_vp]),
     "hb_world_status": (_i, [_vp]),
     "hb_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i]),
+    "hb_all_reduce_add_rms_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i]),
     "hb_fused_rowparallel_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "hb_fused_rowparallel": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f, _i, _vp]),
     "hb_column_shard": (_i, [_vp, _vp, _i64, _i64, _sz, _i, _i]),
@@ -509,6 +510,17 @@ class TpWorld:
         check(lib.hb_all_reduce(self.handle, _stream(stream), _ptr(buf), buf.numel(),
                                 dtype_code(buf.dtype), algo))
         return buf
+
+    def all_reduce_add_rms_norm(self, partial, resid, norm_w, eps: float, algo: int = ALGO_AUTO, stream=None):
+        """(normed, new_resid) = rms_norm(resid + SUM_ranks partial) in one kernel per rank."""
+        import torch
+
+        rows, hidden = partial.shape
+        normed, res = torch.empty_like(resid), torch.empty_like(resid)
+        check(lib.hb_all_reduce_add_rms_norm(self.handle, _stream(stream), _ptr(normed), _ptr(res), _ptr(partial),
+                                             _ptr(resid), _ptr(norm_w), rows, hidden, eps, dtype_code(partial.dtype),
+                                             algo))
+        return normed, res
 
     def fused_rowparallel(self, x, w, resid, norm_w, eps: float, algo: int = ALGO_AUTO, stream=None):
         """(normed, new_resid) = fused o_proj/down_proj + all-reduce + residual + RMSNorm."""

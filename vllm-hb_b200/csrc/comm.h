@@ -48,5 +48,11 @@ namespace hb {
 // In-place all-reduce on `st`; the building block of hb_all_reduce and of the engine.
 int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_dtype dtype,
                      hb_algo algo);
+// All-reduce of `partial` + residual add + RMSNorm in one kernel (ar_norm.cu); the values
+// of world_all_reduce followed by hb_add_rms_norm.
+bool ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
+int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
+                      const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
+                      hb_dtype dtype, hb_algo algo);
 
 }  // namespace hb

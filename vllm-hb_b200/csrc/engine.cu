@@ -435,6 +435,30 @@ static void prof_mark(hb_engine* e, int cat) {
   e->prof_cats.push_back(cat);
 }
 
+// h += SUM_ranks d_proj; x = norm(h; norm_w): one kernel over peer memory when the world has
+// several ranks (HB_AR_NORM=0: all-reduce kernel, then add+norm), add+norm alone otherwise.
+static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B) {
+  int rc;
+  cudaStream_t st = e->stream;
+  const float eps = (float)e->eps;
+  if (e->ws > 1) {
+    static const bool split = [] { const char* v = getenv("HB_AR_NORM"); return v && v[0] == '0'; }();
+    prof_mark(e, kCatComm);
+    if (!split && ar_add_norm_supported(e->world, B, e->H, e->dtype)) {
+      if ((rc = world_ar_add_norm(e->world, st, x_out, e->d_h, e->d_proj, e->d_h, norm_w, B, e->H, eps, e->dtype,
+                                  HB_ALGO_AUTO))) return rc;
+      ++e->last_launches;
+      return HB_OK;
+    }
+    if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
+    ++e->last_launches;
+  }
+  prof_mark(e, kCatNorm);
+  if ((rc = hb_add_rms_norm(st, x_out, e->d_h, e->d_proj, e->d_h, norm_w, B, e->H, eps, e->dtype))) return rc;
+  ++e->last_launches;
+  return HB_OK;
+}
+
 // Issues every kernel of one decode step on e->stream (captured or direct).
 static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   int rc;
@@ -478,14 +502,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       ++e->last_launches;
     } else {
       if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
-      if (e->ws > 1) {
-        prof_mark(e, kCatComm);
-        if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
-        ++e->last_launches;
-      }
-      prof_mark(e, kCatNorm);
-      if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, w.norm_post, B, e->H, eps, e->dtype))) return rc;
-      ++e->last_launches;
+      if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B))) return rc;
     }
     // mixture of experts: routing weights of every token       mixtral.rs:371-412
     if (e->moe) {
@@ -519,14 +536,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       ++e->last_launches;
     } else {
       if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
-      if (e->ws > 1) {
-        prof_mark(e, kCatComm);
-        if ((rc = world_all_reduce(e->world, st, e->d_proj, (size_t)B * e->H, e->dtype, HB_ALGO_AUTO))) return rc;
-        ++e->last_launches;
-      }
-      prof_mark(e, kCatNorm);
-      if ((rc = hb_add_rms_norm(st, e->d_x, e->d_h, e->d_proj, e->d_h, nw, B, e->H, eps, e->dtype))) return rc;
-      ++e->last_launches;
+      if ((rc = reduce_add_norm(e, e->d_x, nw, B))) return rc;
     }
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
