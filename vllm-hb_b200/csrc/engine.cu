@@ -58,6 +58,7 @@ struct StepPlans {
   std::vector<TcGemmPlan> layer;  // [L * 4]
   TcGemmPlan lm_head;
   int attn_splits = 1;
+  bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
   int64_t launches = 0;  // kernels in one step (fixed per batch size)
   cudaGraphExec_t graph = nullptr;
 };
@@ -79,6 +80,8 @@ struct hb_engine {
   int64_t E = 1, topk = 1, window = 0, I_e = 0;
   bool moe = false;
   float* d_scale = nullptr;  // [max_batch, E] routing weights of the step
+  float* d_rowsq = nullptr;  // [max_batch, rowsq_stride] row sums of the deferred norm
+  int rowsq_stride = 0;
   // weights
   void* embed = nullptr;
   void* lm_head = nullptr;
@@ -326,6 +329,9 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = dev_alloc(e, &e->d_gu, (size_t)B * 2 * e->I_e * es))) return rc;
   if ((rc = dev_alloc(e, &e->d_act, (size_t)B * e->I_e * es))) return rc;
   if (e->moe && (rc = dev_alloc(e, (void**)&e->d_scale, (size_t)B * e->E * 4))) return rc;
+  e->rowsq_stride = (int)(((e->H + 127) / 128 + 3) / 4 * 4);
+  if ((rc = dev_alloc(e, (void**)&e->d_rowsq, (size_t)B * e->rowsq_stride * 4))) return rc;
+  HB_CUDA_CHECK(cudaMemset(e->d_rowsq, 0, (size_t)B * e->rowsq_stride * 4));
   if ((rc = dev_alloc(e, &e->d_proj, (size_t)B * e->H * es))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_logits, (size_t)B * e->V * 4))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_next, (size_t)B * 4))) return rc;
@@ -377,20 +383,46 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
   if (e->use_tc) {
     sp.layer.resize(e->L * 4);
     int rc;
+    // Single rank: residual add and RMSNorm ride in the GEMM epilogues (HB_DEFER_NORM=0:
+    // separate add+norm kernels) when o_proj and down_proj get cluster plans.
+    static const bool no_defer = [] { const char* v = getenv("HB_DEFER_NORM"); return v && v[0] == '0'; }();
+    sp.defer_norm = e->ws == 1 && !e->use_fused && !no_defer && e->H % 128 == 0 && !e->moe;  // the router reads normalised x
+    if (sp.defer_norm) {
+      TcGemmPlan probe_o, probe_d;
+      auto& w0 = e->layers[0];
+      if ((rc = gemm_tc_plan(&probe_o, e->d_attn, w0.wo, B, e->H, e->hq_l * e->hd, kEpiResidual, false, e->device))) return rc;
+      if ((rc = gemm_tc_plan(&probe_d, e->d_act, w0.wdown, B, e->H, e->I_e, kEpiResidual, false, e->device))) return rc;
+      sp.defer_norm = probe_o.cluster && probe_d.cluster && probe_o.m_tiles == 1 && probe_d.m_tiles == 1;
+    }
+    const int row_epi = sp.defer_norm ? kEpiResidual : kEpiStore;
     for (int64_t l = 0; l < e->L; ++l) {
       auto& w = e->layers[l];
       if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kQkv], e->d_x, w.wqkv, B, e->qkv_rows, e->H, kEpiStore, false, e->device))) return rc;
-      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kO], e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, kEpiStore, false, e->device))) return rc;
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kO], e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, row_epi, false, e->device))) return rc;
       if (e->fused_swiglu) {
         if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_e, e->H, kEpiSwiGLU, false, e->device))) return rc;
       } else {
         if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kGateUp], e->d_x, w.wgu, B, 2 * e->I_e, e->H, kEpiStore, false, e->device))) return rc;
       }
-      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_e, kEpiStore, false, e->device))) return rc;
+      if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_e, row_epi, false, e->device))) return rc;
       for (int k = 0; k < 4; ++k) ws = std::max(ws, sp.layer[l * 4 + k].workspace_bytes());
     }
     if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
     ws = std::max(ws, sp.lm_head.workspace_bytes());
+    if (sp.defer_norm) {
+      auto can_scale = [](const TcGemmPlan& pl) { return pl.tma_store && (pl.cluster || pl.splits == 1) && pl.m_tiles == 1; };
+      bool ok = can_scale(sp.lm_head);
+      for (int64_t l = 0; l < e->L && ok; ++l)
+        ok = can_scale(sp.layer[l * 4 + kQkv]) && can_scale(sp.layer[l * 4 + kGateUp]) && e->fused_swiglu;
+      if (!ok) {  // re-plan the row-parallel projections with the plain epilogue
+        sp.defer_norm = false;
+        for (int64_t l = 0; l < e->L; ++l) {
+          auto& w = e->layers[l];
+          if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kO], e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, kEpiStore, false, e->device))) return rc;
+          if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kDown], e->d_act, w.wdown, B, e->H, e->I_e, kEpiStore, false, e->device))) return rc;
+        }
+      }
+    }
   }
   if (ws > e->gemm_ws_bytes) {
     // grows only when a new batch size needs more; never inside a captured step
@@ -410,11 +442,11 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
 }
 
 static int run_gemm(hb_engine* e, StepPlans* sp, int64_t l, int kind, void* Y, const void* X,
-                    const void* W, int B, int64_t N, int64_t K, bool out_f32) {
+                    const void* W, int B, int64_t N, int64_t K, bool out_f32, const TcNormLink* link = nullptr) {
   ++e->last_launches;
   if (e->use_tc) {
     const TcGemmPlan& pl = (kind == kLmHead) ? sp->lm_head : sp->layer[l * 4 + kind];
-    return gemm_tc_run(pl, e->stream, Y, pl.N, e->d_gemm_ws, e->d_err);
+    return gemm_tc_run(pl, e->stream, Y, pl.N, e->d_gemm_ws, e->d_err, link);
   }
   return gemm_simt(e->stream, Y, X, W, B, N, K, e->dtype, out_f32);
 }
@@ -477,11 +509,20 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   prof_mark(e, kCatNorm);
   if ((rc = hb_rms_norm(st, e->d_x, e->d_h, e->layers[0].norm_in, B, e->H, eps, e->dtype))) return rc;
   e->last_launches += 2;
+  // deferred norm: the GEMM after a row-parallel projection scales its rows (TcNormLink)
+  const bool defer = e->use_tc && sp->defer_norm;
+  TcNormLink consume;
+  consume.rowsq_in = e->d_rowsq;
+  consume.rowsq_tiles = (int)(e->H / 128);
+  consume.rowsq_stride = e->rowsq_stride;
+  consume.n = (float)e->H;
+  consume.eps = eps;
   for (int64_t l = 0; l < e->L; ++l) {
     auto& w = e->layers[l];
     // q|k|v = x . Wqkv^T                                      llama_tp.rs:232-234
     prof_mark(e, kCatGemm);
-    if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false))) return rc;
+    if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false,
+                       (defer && l > 0) ? &consume : nullptr))) return rc;
     // RoPE + KV append                                        llama_tp.rs:242-259
     prof_mark(e, kCatRopeKv);
     if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
@@ -500,6 +541,12 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_attn, w.wo, e->d_h, w.norm_post, B, e->H,
                              e->hq_l * e->hd, eps, HB_ALGO_AUTO, e->d_fused_ws))) return rc;
       ++e->last_launches;
+    } else if (defer) {
+      // h += o_proj(attn); x' = h * w_post; row sums for the gate|up GEMM
+      TcNormLink produce;
+      produce.resid = e->d_h; produce.norm_w = w.norm_post; produce.rowsq_out = e->d_rowsq;
+      produce.rowsq_stride = e->rowsq_stride;
+      if ((rc = run_gemm(e, sp, l, kO, e->d_x, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false, &produce))) return rc;
     } else {
       if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
       if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B))) return rc;
@@ -513,7 +560,8 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
     prof_mark(e, kCatGemmGateUp);
     if (e->use_tc && e->fused_swiglu) {
-      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false))) return rc;
+      if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false,
+                         defer ? &consume : nullptr))) return rc;
     } else {
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false))) return rc;
       prof_mark(e, kCatOther);
@@ -534,6 +582,11 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_e, eps,
                              HB_ALGO_AUTO, e->d_fused_ws))) return rc;
       ++e->last_launches;
+    } else if (defer) {
+      TcNormLink produce;
+      produce.resid = e->d_h; produce.norm_w = nw; produce.rowsq_out = e->d_rowsq;
+      produce.rowsq_stride = e->rowsq_stride;
+      if ((rc = run_gemm(e, sp, l, kDown, e->d_x, e->d_act, w.wdown, B, e->H, e->I_e, false, &produce))) return rc;
     } else {
       if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
       if ((rc = reduce_add_norm(e, e->d_x, nw, B))) return rc;
@@ -541,7 +594,8 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107
   prof_mark(e, kCatGemmLmHead);
-  if ((rc = run_gemm(e, sp, 0, kLmHead, e->d_logits, e->d_x, e->lm_head, B, e->V, e->H, true))) return rc;
+  if ((rc = run_gemm(e, sp, 0, kLmHead, e->d_logits, e->d_x, e->lm_head, B, e->V, e->H, true,
+                     defer ? &consume : nullptr))) return rc;
   prof_mark(e, kCatOther);
   if ((rc = hb_argmax(st, e->d_next, e->d_logits, B, e->V, HB_F32))) return rc;
   ++e->last_launches;

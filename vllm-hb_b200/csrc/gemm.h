@@ -15,6 +15,29 @@ int gemm_simt(cudaStream_t st, void* Y, const void* X, const void* W, int64_t M,
 enum TcEpilogue : int {
   kEpiStore = 0,     // Y = acc (bf16, or f32 when out_f32)
   kEpiSwiGLU = 1,    // W rows are [gate tile | up tile] pairs: Y = silu(gate) * up, N_out = N/2
+  kEpiResidual = 2,  // deferred RMSNorm producer (cluster plans only), see TcNormLink
+};
+
+// Deferred RMSNorm between two GEMMs of a single-rank decode step.  Instead of a separate
+// add + norm kernel between a row-parallel projection P and the projection C that consumes
+// the normalised activations, P's epilogue (kEpiResidual) writes
+//     h  = resid + Y                      (the new residual, in place in `resid`)
+//     Y' = h * norm_w                     (what C reads as its X operand)
+//     rowsq[m][tile] = sum over the tile's 128 features of h[m]^2
+// and C multiplies batch row m of its accumulator by rsqrt(sum_tiles rowsq[m][.] / n + eps)
+// before its own epilogue:  (h * r * w) . W^T == r * ((h * w) . W^T).  The only numerical
+// difference from normalising first is where the single bf16 rounding of the activations
+// falls (h*w instead of h*r*w).
+struct TcNormLink {
+  // producer side (kEpiResidual)
+  void* resid = nullptr;           // [M, N] bf16, read and overwritten with h
+  const void* norm_w = nullptr;    // [N] bf16
+  float* rowsq_out = nullptr;      // [M, rowsq_stride] fp32
+  // consumer side
+  const float* rowsq_in = nullptr; // [M, rowsq_stride] fp32 written by the producer
+  int rowsq_tiles = 0;             // entries to sum per row = producer's N / 128
+  int rowsq_stride = 0;
+  float n = 1.f, eps = 0.f;        // mean over n features
 };
 
 // A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by
@@ -47,6 +70,6 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
 // Y row stride ldy in elements.  workspace: plan.workspace_bytes(), zeroed once.
 // err_flag (device int, may be null) is set non-zero when a bounded wait ran out.
 int gemm_tc_run(const TcGemmPlan& plan, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
-                int* err_flag);
+                int* err_flag, const TcNormLink* link = nullptr);
 
 }  // namespace hb

@@ -41,6 +41,16 @@ struct TcParams {
   int stagger;              // rotate the K walk per tile
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
   int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
+  // Deferred RMSNorm (see TcNormLink in gemm.h).  Producer (epilogue kEpiResidual, cluster
+  // form only): h = resid + Y, written through tm_h; Y' = h * norm_w written through tm_y;
+  // row sums of h^2 over this tile's 128 features to rowsq_out[row * rowsq_stride + tile].
+  // Consumer (rowsq_in != null): every accumulator column (batch row) is multiplied by
+  // rsqrt(sum over rowsq_tiles entries / rs_n + rs_eps) before the epilogue.
+  const __nv_bfloat16* norm_w;
+  float* rowsq_out;
+  const float* rowsq_in;
+  int rowsq_stride, rowsq_tiles;
+  float rs_inv_n, rs_eps;
   void* Y;
   float* partials;
   int* counters;
@@ -75,7 +85,8 @@ __device__ __forceinline__ void tc_trace(int slot) {
 // ----------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-               const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
+               const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_h,
+               const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
@@ -83,6 +94,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_last;
+  __shared__ __align__(8) uint64_t s_resid;  // residual tile landed (kEpiResidual)
+  __shared__ float s_rscale[256];            // row scales of the deferred norm (consumer)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool swiglu = p.epilogue == kEpiSwiGLU;
@@ -109,6 +122,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     mbar_init(smem_u32(&s_done), 1);
+    mbar_init(smem_u32(&s_resid), 1);
     s_abort = 0;
     s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,6 +143,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   pdl_launch_dependents();  // the next kernel may start its own prologue / weight prefetch
   if (!(warp == 0 && lane == 0)) pdl_wait();  // the producer waits after its weight prefetch
 
+  if (warp >= 2 && p.rowsq_in) {
+    // deferred norm: scale of every batch row of this tile column, from the row sums the
+    // producing GEMM left per 128-feature tile (fixed summation order)
+    for (int i = tid - 64; i < p.m_pad; i += 64) {
+      const int m = blockIdx.y * p.m_pad + i;
+      float sc = 1.f;
+      if (m < p.M) {
+        // rows are padded to a multiple of four entries that stay zero: 128-bit loads,
+        // all in flight at once, summed in a fixed order
+        const float4* rq = reinterpret_cast<const float4*>(p.rowsq_in + (int64_t)m * p.rowsq_stride);
+        const int n4 = (p.rowsq_tiles + 3) >> 2;
+        float a = 0.f;
+#pragma unroll 8
+        for (int t4 = 0; t4 < n4; ++t4) {
+          const float4 v = __ldcg(rq + t4);
+          a += (v.x + v.y) + (v.z + v.w);
+        }
+        sc = rsqrtf(a * p.rs_inv_n + p.rs_eps);
+      }
+      s_rscale[i] = sc;
+    }
+  }
   if (warp == 0) {
     if (lane == 0) {
       // ---------------------------------------------------------- TMA producer
@@ -246,6 +282,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][n_acc][CW/4][128 features][4 columns]
     const int slot_floats = n_acc * CW * kTileN;
     const uint32_t out_off = (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
+    const bool residual = p.epilogue == kEpiResidual;
+    const uint32_t tile_b = (uint32_t)CW * kTileN * 2u;   // one staged bf16 tile
+    const uint32_t h_off = out_off + tile_b;              // kEpiResidual: new residual [CW][128]
+    const uint32_t resid_off = h_off + tile_b;            // kEpiResidual: residual tile read by TMA
+    if (residual && tid == 0 && ok_all) {
+      // this CTA's own pipeline buffers are idle: fetch the residual tile while the partners
+      // catch up and exchange (rows past the batch read as zeros)
+      const uint32_t bar = smem_u32(&s_resid);
+      mbar_expect_tx(bar, tile_b);
+      tma_load_2d(smem_base + resid_off, &tm_h, tile * kTileN, m_base + split * CW, bar);
+    }
     cluster_sync_all();  // every partner's pipeline buffers are idle from here on
     TC_TRACE(tid == 0, 5);
     if (ok_all) {
@@ -272,6 +319,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
     TC_TRACE(tid == 0, 6);
+    bool resid_ok = true;
+    const float w_norm = (residual && n_glob < p.N) ? __bfloat162float(p.norm_w[n_glob]) : 0.f;
     if (ok_all) {
       const int c_lo = split * CW;
       for (int c0 = c_lo & ~15; c0 < c_lo + CW; c0 += 16) {
@@ -306,27 +355,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             }
           }
         }
+        if (p.rowsq_in) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float rs_ = s_rscale[c0 + j];
+            g[j] *= rs_;
+            u[j] *= rs_;
+          }
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = swiglu ? silu_f(g[j]) * u[j] : g[j];
+        if (residual) {
+          // h = resid + Y (both rounded to bf16 as the reference materialises them); the
+          // norm weight is applied here, the row scale by the GEMM that consumes Y'
+          if (c0 == (c_lo & ~15)) resid_ok = mbar_wait(smem_u32(&s_resid), 0, &s_abort);
+          const __nv_bfloat16* rs_tile = reinterpret_cast<const __nv_bfloat16*>(smem_gen + resid_off);
+          __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(smem_gen + h_off);
+          __nv_bfloat16* ts = reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int cl = c0 + j - c_lo;
-          if (cl >= 0 && cl < CW) {
-            if (p.out_f32) reinterpret_cast<float*>(smem_gen + out_off)[cl * kTileN + row] = g[j];
-            else reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off)[cl * kTileN + row] = __float2bfloat16_rn(g[j]);
+          for (int j = 0; j < 16; ++j) {
+            const int cl = c0 + j - c_lo;
+            if (cl >= 0 && cl < CW) {
+              const float y = __bfloat162float(__float2bfloat16_rn(g[j]));
+              const __nv_bfloat16 h = __float2bfloat16_rn(__bfloat162float(rs_tile[cl * kTileN + row]) + y);
+              hs[cl * kTileN + row] = h;
+              ts[cl * kTileN + row] = __float2bfloat16_rn(__bfloat162float(h) * w_norm);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int cl = c0 + j - c_lo;
+            if (cl >= 0 && cl < CW) {
+              if (p.out_f32) reinterpret_cast<float*>(smem_gen + out_off)[cl * kTileN + row] = g[j];
+              else reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off)[cl * kTileN + row] = __float2bfloat16_rn(g[j]);
+            }
           }
         }
       }
       fence_async_smem();
     }
     TC_TRACE(tid == 0, 10);
-    __syncthreads();
+    const bool tail_ok = __syncthreads_and((ok_all && resid_ok) ? 1 : 0) != 0;
     TC_TRACE(tid == 0, 11);
-    if (ok_all && tid == 0 && m_base + split * CW < p.M) {
+    if (tail_ok && residual) {
+      // sum of squares of every new residual row over this tile's 128 features: a warp per
+      // row, four values per lane, fixed order
+      const __nv_bfloat16* hs = reinterpret_cast<const __nv_bfloat16*>(smem_gen + h_off);
+      for (int cl = warp; cl < CW; cl += kTcThreads / 32) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(hs + cl * kTileN + lane * 4);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+        float ss = (a.x * a.x + a.y * a.y) + (b.x * b.x + b.y * b.y);
+        ss = warp_sum(ss);
+        const int m = m_base + split * CW + cl;
+        if (lane == 0 && m < p.M) p.rowsq_out[(int64_t)m * p.rowsq_stride + tile] = ss;
+      }
+    }
+    if (tail_ok && tid == 0 && m_base + split * CW < p.M) {
       tma_store_2d(&tm_y, smem_base + out_off, tile * kTileN, m_base + split * CW);
+      if (residual) tma_store_2d(&tm_h, smem_base + h_off, tile * kTileN, m_base + split * CW);
       tma_store_commit();
       tma_store_wait_read();
     }
+    if (!tail_ok && ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
     TC_TRACE(tid == 0, 12);
     if (!ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
   } else if (ok_all && p.splits == 1 && p.tma_store) {
@@ -345,9 +437,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       for (int g = g0; g < g1; ++g) {
         float v[16];
         tmem_ld16(t_lane + g * 16, v);
+        if (p.rowsq_in) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] *= s_rscale[g * 16 + j];
+        }
         if (swiglu) {
           float u[16];
           tmem_ld16(t_lane + p.m_pad + g * 16, u);
+          if (p.rowsq_in) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) u[j] *= s_rscale[g * 16 + j];
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = silu_f(v[j]) * u[j];
         }
@@ -589,7 +689,8 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   auto recv_fits = [&](int sp) {
     // received partials [sp-1][n_acc][m_pad/sp][128] fp32 + the staged output [m_pad/sp][128]
     const size_t cw = (size_t)pl.m_pad / sp;
-    return (size_t)(sp - 1) * n_acc * cw * kTileN * sizeof(float) + cw * kTileN * out_elt <=
+    const size_t extra = epilogue == kEpiResidual ? 2 * cw * kTileN * 2 : 0;  // new residual + fetched residual
+    return (size_t)(sp - 1) * n_acc * cw * kTileN * sizeof(float) + cw * kTileN * out_elt + extra <=
            (size_t)pl.stages * stage;
   };
   if (want_cluster && pl.splits > 1 && pl.tma_store) {
@@ -637,9 +738,9 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     if (cur >= 0 && cur < 64 && !dev_done[cur]) {
-      // 227 KiB per CTA minus the kernel's static shared memory (barriers, flags)
+      // 227 KiB per CTA minus the kernel's static shared memory (barriers, flags, row scales)
       HB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         226 * 1024));
+                                         224 * 1024));
       dev_done[cur] = true;
     }
   }
@@ -651,11 +752,12 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
 }
 
 int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
-                int* err_flag) {
+                int* err_flag, const TcNormLink* link) {
   if (pl.splits > 1 && !pl.cluster && !workspace)
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: split-K plan needs a workspace of %zu bytes",
                 pl.workspace_bytes());
   TcParams p;
+  memset(&p, 0, sizeof(p));
   p.M = (int)pl.M; p.N = (int)pl.N;
   p.m_pad = pl.m_pad; p.splits = pl.splits; p.stages = pl.stages; p.tmem_cols = pl.tmem_cols;
   p.k_chunks = (int)(pl.K / kTileK);
@@ -682,6 +784,28 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
     int rc = encode_out_map(&tm_y, Y, pl.M, pl.N, ldy, pl.out_f32, box_rows);
     if (rc) return rc;
   }
+  CUtensorMap tm_h;
+  memset(&tm_h, 0, sizeof(tm_h));
+  if (pl.epilogue == kEpiResidual) {
+    if (!pl.cluster || !p.tma_store || pl.out_f32 || !link || !link->resid || !link->norm_w || !link->rowsq_out)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the residual epilogue needs a cluster plan, bf16 output and a norm link");
+    if ((reinterpret_cast<uintptr_t>(link->resid) & 15) || link->rowsq_stride < pl.n_tiles)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: bad residual buffer or row-sum stride");
+    int rc = encode_out_map(&tm_h, link->resid, pl.M, pl.N, ldy, false, pl.m_pad / pl.splits);
+    if (rc) return rc;
+    p.norm_w = (const __nv_bfloat16*)link->norm_w;
+    p.rowsq_out = link->rowsq_out;
+    p.rowsq_stride = link->rowsq_stride;
+  }
+  if (link && link->rowsq_in) {
+    if (!p.tma_store || (pl.splits > 1 && !pl.cluster))
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: row scaling needs the bulk-store epilogue");
+    p.rowsq_in = link->rowsq_in;
+    p.rowsq_tiles = link->rowsq_tiles;
+    p.rowsq_stride = link->rowsq_stride;
+    p.rs_inv_n = 1.0f / link->n;
+    p.rs_eps = link->eps;
+  }
   { const char* sg = getenv("HB_TC_STAGGER"); p.stagger = (sg && sg[0] == '1') ? 1 : 0; }  // measured: no gain, off
   dim3 grid((unsigned)(pl.n_tiles * pl.splits), (unsigned)pl.m_tiles);
   cudaLaunchConfig_t cfg = {};
@@ -706,7 +830,7 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, pl.tm_w, pl.tm_x, tm_y, p));
+  HB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel, pl.tm_w, pl.tm_x, tm_y, tm_h, p));
   return HB_OK;
 }
 
