@@ -8,6 +8,7 @@ Shapes: X [M, K/TP] ~N(0,1), W [N, K/TP] ~N(0,0.02) per rank, residual [M, N] ~N
 norm weight ones, eps 1e-5; M in {1, 8, 64, 256}; (K, N) = (28672, 8192) (down_proj) and
 (8192, 8192) (o_proj).  Variants timed per point:
     fused      hb_fused_rowparallel (auto / one-shot / two-shot)
+    gemm_arn   hb_gemm -> hb_all_reduce_add_rms_norm (one peer-memory kernel: what the engine runs)
     unfused    hb_gemm -> hb_all_reduce (peer memory) -> hb_add_rms_norm
     baseline   torch.matmul (cuBLAS) -> NCCL all_reduce -> hb_add_rms_norm: the
                reference's sequence (src/engine/arch/llama_tp.rs:327,533-552)
@@ -93,6 +94,11 @@ def main() -> None:
                 hb.check(hb.lib.hb_add_rms_norm(st, out[0].data_ptr(), out[1].data_ptr(), part.data_ptr(), resid.data_ptr(),
                                                 nw.data_ptr(), M, N, 1e-5, hb.BF16))
 
+            def gemm_arn(i):
+                hb.check(hb.lib.hb_gemm(st, part.data_ptr(), x.data_ptr(), ws[i].data_ptr(), M, N, Kl, hb.BF16, gws.data_ptr()))
+                hb.check(hb.lib.hb_all_reduce_add_rms_norm(tp.handle, st, out[0].data_ptr(), out[1].data_ptr(), part.data_ptr(),
+                                                           resid.data_ptr(), nw.data_ptr(), M, N, 1e-5, hb.BF16, hb.ALGO_AUTO))
+
             def baseline(i):
                 p2 = torch.matmul(x, ws[i].t())
                 if world > 1:
@@ -105,6 +111,8 @@ def main() -> None:
             if world > 1:
                 row["fused_one_shot_us"] = timed(fused(hb.ALGO_ONE_SHOT), 4)
                 row["fused_two_shot_us"] = timed(fused(hb.ALGO_TWO_SHOT), 4)
+            if world > 1:
+                row["gemm_arn_us"] = timed(gemm_arn, 4)
             row["unfused_us"] = timed(unfused, 4)
             row["baseline_cublas_nccl_us"] = timed(baseline, 4)
             hbm_bytes = 2 * (Kl * N + M * Kl + 3 * M * N + N)
@@ -112,8 +120,8 @@ def main() -> None:
             row["hbm_bytes"], row["nvlink_bytes_per_dir"] = hbm_bytes, nvl_bytes
             roof_us = max(hbm_bytes / hbm / 1e3, nvl_bytes / nvl / 1e3)
             row["roofline_us"] = roof_us
-            best = min(v for k, v in row.items() if k.startswith("fused_"))
-            row["fused_frac_of_roofline"] = roof_us / best
+            best = min(v for k, v in row.items() if k.startswith("fused_") or k == "gemm_arn_us")
+            row["best_frac_of_roofline"] = roof_us / best
             row["speedup_vs_baseline"] = row["baseline_cublas_nccl_us"] / best
             row["speedup_vs_unfused"] = row["unfused_us"] / best
             if tp is not None and tp.status() != 0:

@@ -25,8 +25,11 @@
 
 namespace hb {
 
-constexpr int kAnThreads = 512;
-constexpr int kAnMaxVec = 4;  // 16-byte vectors per thread kept in registers
+// Thread count, vector assignment (v = tid + i * threads) and the order of the row
+// sum are those of rms_norm_vec_kernel (norm.cu), so that the normalised row is
+// bit-identical to hb_add_rms_norm's.
+constexpr int kAnThreads = 256;
+constexpr int kAnMaxVec = 8;  // 16-byte vectors per thread kept in registers
 constexpr uint32_t kAnSpin = 1u << 22;
 
 __device__ __forceinline__ uint32_t an_ld_acquire(const uint32_t* p) {
@@ -58,7 +61,7 @@ struct ArNormParams {
   int rows_own;          // two-shot: rows a rank reduces = ceil(M / R); one-shot: M
   int64_t gather_off;    // two-shot: vector offset of the gathered rows inside the data area
   float eps;
-  float inv_n;
+  float n_feat;
 };
 
 template <typename T>
@@ -176,7 +179,7 @@ ar_add_norm_kernel(const ArNormParams p) {
   // row scale and the normalised row (numerics of rms_norm_vec_kernel)
   ss = block_sum(ss, s_red);
   if (all_ok && p.normed_out) {
-    const float scale = rsqrtf(ss * p.inv_n + p.eps);
+    const float scale = rsqrtf(ss / p.n_feat + p.eps);
     uint4* nout = reinterpret_cast<uint4*>(p.normed_out) + (int64_t)row * rv;
     const uint4* wv = reinterpret_cast<const uint4*>(p.norm_w);
 #pragma unroll
@@ -244,7 +247,7 @@ int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resi
   p.rows_own = two ? (int)((M + R - 1) / R) : (int)M;
   p.gather_off = (int64_t)R * p.rows_own * p.row_vecs;
   p.eps = eps;
-  p.inv_n = 1.0f / (float)N;
+  p.n_feat = (float)N;
   const size_t need = ((size_t)p.gather_off + (two ? (size_t)M * p.row_vecs : 0)) * 16;
   if (need > w->staging_bytes)
     return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: needs %zu bytes of staging, world has %zu", need,
