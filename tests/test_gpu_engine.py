@@ -132,14 +132,18 @@ def fetch_weights(eng, cfg):
     return out
 
 
-@pytest.mark.parametrize("fused", ["0", "1"])
+@pytest.mark.parametrize("fused", ["0", "1", "rope"])
 @pytest.mark.parametrize("norm_ones", [True, False])
 def test_random_init_bf16_tensor_core_path(hb, cuda, norm_ones, fused, monkeypatch):
     """Device-initialised bf16 model on the tcgen05 GEMM path; the oracle runs on the
     very weights read back from the device.  fused=1 routes o_proj / down_proj through
     the one-kernel GEMM + reduce + residual + norm (the engine reads HB_FUSED when it is
-    created), fused=0 through GEMM, all-reduce and add+norm kernels."""
-    monkeypatch.setenv("HB_FUSED", fused)
+    created), fused=0 through the default path, "rope" additionally with RoPE and the KV
+    append fused into the attention kernel."""
+    if fused == "rope":  # RoPE and the KV append inside the attention kernel
+        monkeypatch.setenv("HB_FUSE_ROPE", "1")
+    else:
+        monkeypatch.setenv("HB_FUSED", fused)
     eng = hb.Engine.create_random(SHAPE_TC, seed=1, std=0.02, norm_ones=norm_ones, max_seq_len=128,
                                   bf16=True, max_batch=16)
     cfg = R.LlamaTpConfig(**SHAPE_TC)

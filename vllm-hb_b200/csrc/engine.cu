@@ -113,6 +113,7 @@ struct hb_engine {
   size_t gemm_ws_bytes = 0;
   int* d_err = nullptr;
   bool use_tc = false, use_graph = true, fused_swiglu = true, use_fused = false;
+  bool fuse_rope = false;  // RoPE + KV append inside the tensor-core attention kernel
   void* d_fused_ws = nullptr;
   std::map<int, hb::StepPlans> plans;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -342,6 +343,15 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = dev_alloc(e, (void**)&e->d_inv_freq, inv.size() * 4))) return rc;
   HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
   if ((rc = paged_attention_mma_prepare())) return rc;
+  {
+    // Off by default: measured inside the step's CUDA graph, the rotation and the append at
+    // the head of every attention CTA delay its first KV loads by more than the separate
+    // 6 us kernel costs (4.78 against 4.74 ms per step on the 8B shape).  HB_FUSE_ROPE=1 enables it.
+    const char* fr = getenv("HB_FUSE_ROPE");
+    e->fuse_rope = fr && fr[0] == '1' && !getenv("HB_ATTN") &&
+                   paged_attention_mma_supported(e->d_qkv, e->qkv_rows, e->kc[0], e->vc[0], (int)(e->hq_l / e->hkv_l),
+                                                 (int)e->hd, e->num_blocks, (int)e->hkv_l, e->dtype);
+  }
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
   // The row-parallel projections run as GEMM -> peer-memory all-reduce -> add+norm by
@@ -524,16 +534,19 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false,
                        (defer && l > 0) ? &consume : nullptr))) return rc;
     // RoPE + KV append                                        llama_tp.rs:242-259
-    prof_mark(e, kCatRopeKv);
-    if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
-                            (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;
+    if (!e->fuse_rope) {
+      prof_mark(e, kCatRopeKv);
+      if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
+                              (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;
+      ++e->last_launches;
+    }
     // softmax(q k^T / sqrt d) v over the block table          llama_tp.rs:264-324
     prof_mark(e, kCatAttention);
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype, e->d_err, (int)e->window))) return rc;
-    e->last_launches += 2 + (sp->attn_splits > 1 ? 1 : 0);
+                              e->dtype, e->d_err, (int)e->window, e->fuse_rope ? e->d_inv_freq : nullptr))) return rc;
+    e->last_launches += 1 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);
     if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->hq_l * e->hd)) {
