@@ -123,6 +123,9 @@ def test_engine_errors(hb, cuda, tiny, tmp_path):
 
 SHAPE_TC = dict(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
                 num_key_value_heads=2, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=500000.0)
+# head_dim 128: the tensor-core attention kernel (head_dim 64 above runs the CUDA-core one)
+SHAPE_TC128 = dict(hidden_size=1024, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                   num_key_value_heads=2, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=500000.0)
 
 
 def fetch_weights(eng, cfg):
@@ -144,9 +147,10 @@ def test_random_init_bf16_tensor_core_path(hb, cuda, norm_ones, fused, monkeypat
         monkeypatch.setenv("HB_FUSE_ROPE", "1")
     else:
         monkeypatch.setenv("HB_FUSED", fused)
-    eng = hb.Engine.create_random(SHAPE_TC, seed=1, std=0.02, norm_ones=norm_ones, max_seq_len=128,
+    shape = SHAPE_TC128 if fused == "rope" or not norm_ones else SHAPE_TC
+    eng = hb.Engine.create_random(shape, seed=1, std=0.02, norm_ones=norm_ones, max_seq_len=128,
                                   bf16=True, max_batch=16)
-    cfg = R.LlamaTpConfig(**SHAPE_TC)
+    cfg = R.LlamaTpConfig(**shape)
     weights = fetch_weights(eng, cfg)
     w = weights["model.layers.0.mlp.down_proj.weight"]
     assert abs(float(w.std()) - 0.02) < 2e-3 and abs(float(w.mean())) < 1e-3
