@@ -40,6 +40,7 @@ struct TcParams {
   int packed;               // weights stored tile-major: [n_tile][k_chunk][128][64]
   int stagger;              // rotate the K walk per tile
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
+  int bulk;                 // cluster exchange by bulk copies into a dedicated receive area
   int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
   // Deferred RMSNorm (see TcNormLink in gemm.h).  Producer (epilogue kEpiResidual, cluster
   // form only): h = resid + Y, written through tm_h; Y' = h * norm_w written through tm_y;
@@ -95,6 +96,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __shared__ int s_abort;
   __shared__ int s_last;
   __shared__ __align__(8) uint64_t s_resid;  // residual tile landed (kEpiResidual)
+  __shared__ __align__(8) uint64_t s_recv;   // partners' partials landed (bulk exchange)
   __shared__ float s_rscale[256];            // row scales of the deferred norm (consumer)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -123,6 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     mbar_init(smem_u32(&s_done), 1);
     mbar_init(smem_u32(&s_resid), 1);
+    mbar_init(smem_u32(&s_recv), 1);
     s_abort = 0;
     s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -139,6 +142,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
+  if (p.bulk) {
+    // partners complete bytes on this CTA's barrier: arm it, then make sure every CTA of the
+    // cluster has an initialised barrier before anyone can send
+    if (tid == 0)
+      mbar_expect_tx(smem_u32(&s_recv), (uint32_t)(p.splits - 1) * (uint32_t)(n_acc * (p.m_pad / p.splits) * kTileN * 4));
+    cluster_sync_all();
+  }
   TC_TRACE(tid == 0, 1);
   pdl_launch_dependents();  // the next kernel may start its own prologue / weight prefetch
   if (!(warp == 0 && lane == 0)) pdl_wait();  // the producer waits after its weight prefetch
@@ -279,7 +289,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // partials in split order (deterministic) and runs the epilogue for its rows.
     // Both cluster barriers are reached unconditionally.
     const int S = p.splits, CW = p.m_pad / S;          // CW is a multiple of 4
-    float* recv = reinterpret_cast<float*>(smem_gen);  // [S-1][n_acc][CW/4][128 features][4 columns]
+    // receive area [S-1][n_acc][CW/4][128 features][4 columns]: over the idle pipeline buffers,
+    // or (bulk exchange) a dedicated area behind them so that partners need not wait for
+    // this CTA's pipeline to drain
+    const uint32_t recv_byte_off = p.bulk ? (uint32_t)p.stages * stage_bytes : 0u;
+    float* recv = reinterpret_cast<float*>(smem_gen + recv_byte_off);
     const int slot_floats = n_acc * CW * kTileN;
     const uint32_t out_off = (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
     const bool residual = p.epilogue == kEpiResidual;
@@ -293,9 +307,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_expect_tx(bar, tile_b);
       tma_load_2d(smem_base + resid_off, &tm_h, tile * kTileN, m_base + split * CW, bar);
     }
-    cluster_sync_all();  // every partner's pipeline buffers are idle from here on
+    if (!p.bulk) cluster_sync_all();  // every partner's pipeline buffers are idle from here on
     TC_TRACE(tid == 0, 5);
-    if (ok_all) {
+    if (ok_all && p.bulk) {
+      // stage the columns of every other owner in this CTA's own (idle) pipeline buffers,
+      // then one bulk copy per partner moves them into its receive area
+      for (int acc = 0; acc < n_acc; ++acc) {
+        for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+          if (c0 / CW == split && (c0 + 15) / CW == split) continue;
+          float v[16];
+          tmem_ld16(t_lane + acc * p.m_pad + c0, v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int c = c0 + 4 * q, owner = c / CW;
+            if (owner != split) {
+              const int o_idx = owner < split ? owner : owner - 1;
+              float4* dst = reinterpret_cast<float4*>(smem_gen) +
+                            (o_idx * slot_floats / 4 + (acc * (CW >> 2) + ((c % CW) >> 2)) * kTileN + row);
+              *dst = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+          }
+        }
+      }
+      fence_async_smem();
+    }
+    if (p.bulk) {
+      __syncthreads();
+      if (ok_all && tid == 0) {
+        const uint32_t slot_bytes = (uint32_t)slot_floats * 4u;
+        for (int owner = 0; owner < S; ++owner) {
+          if (owner == split) continue;
+          const int o_idx = owner < split ? owner : owner - 1;
+          const int my_slot = split < owner ? split : split - 1;
+          bulk_copy_to_partner(cluster_map(smem_base + recv_byte_off + (uint32_t)my_slot * slot_bytes, (uint32_t)owner),
+                               smem_base + (uint32_t)o_idx * slot_bytes, slot_bytes,
+                               cluster_map(smem_u32(&s_recv), (uint32_t)owner));
+        }
+        // and wait for the S-1 partials addressed to this CTA
+        if (!mbar_wait(smem_u32(&s_recv), 0, &s_abort)) s_abort = 1;
+      }
+      __syncthreads();
+    }
+    if (ok_all && !p.bulk) {
       for (int acc = 0; acc < n_acc; ++acc) {
         for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
           // groups this CTA owns entirely stay in tensor memory (uniform over the CTA)
@@ -317,9 +370,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
       }
     }
-    cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
+    if (!p.bulk) cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
     TC_TRACE(tid == 0, 6);
-    bool resid_ok = true;
+    bool resid_ok = !(p.bulk && s_abort);
     const float w_norm = (residual && n_glob < p.N) ? __bfloat162float(p.norm_w[n_glob]) : 0.f;
     if (ok_all) {
       const int c_lo = split * CW;
@@ -368,7 +421,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (residual) {
           // h = resid + Y (both rounded to bf16 as the reference materialises them); the
           // norm weight is applied here, the row scale by the GEMM that consumes Y'
-          if (c0 == (c_lo & ~15)) resid_ok = mbar_wait(smem_u32(&s_resid), 0, &s_abort);
+          if (c0 == (c_lo & ~15)) {
+            const bool landed = mbar_wait(smem_u32(&s_resid), 0, &s_abort);
+            resid_ok = resid_ok && landed;
+          }
           const __nv_bfloat16* rs_tile = reinterpret_cast<const __nv_bfloat16*>(smem_gen + resid_off);
           __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(smem_gen + h_off);
           __nv_bfloat16* ts = reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off);
@@ -419,6 +475,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       tma_store_wait_read();
     }
     if (!tail_ok && ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
+    // bulk exchange: a partner's copy engine may still be reading this CTA's staging until
+    // that partner has seen all its bytes; nobody leaves before everybody has
+    if (p.bulk) cluster_sync_all();
     TC_TRACE(tid == 0, 12);
     if (!ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
   } else if (ok_all && p.splits == 1 && p.tma_store) {
@@ -629,6 +688,13 @@ static int pick_splits(int units, int k_chunks, int slots) {
 // shared memory).  One SM draws at most ~34 GB/s of weights from HBM (measured), so
 // every GEMM wants at least one CTA on each SM: the smallest power of two that
 // covers the SMs, at most 8 (portable cluster size), each CTA keeping >= 4 K chunks.
+// HB_TC_BULK=1 selects the bulk-copy exchange (see TcParams::bulk); the default is the
+// 16-byte remote-store exchange.
+static bool bulk_exchange_enabled() {
+  const char* e = getenv("HB_TC_BULK");
+  return e && e[0] == '1';
+}
+
 static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
   int s = 1;
   while (s < 8 && units * s < sm_count && k_chunks / (s * 2) >= 4) s *= 2;
@@ -722,6 +788,25 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
                  pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
+  // Bulk exchange: the partners' partials land in a dedicated area behind the pipeline
+  // buffers (no barrier before sending), moved by one bulk copy per partner.  Taken when
+  // pipeline + receive area still fit the shared-memory budget of the plan.
+  pl.bulk = false;
+  if (pl.cluster && bulk_exchange_enabled()) {
+    const size_t cw = (size_t)pl.m_pad / pl.splits;
+    const size_t recv_bytes = (size_t)(pl.splits - 1) * n_acc * cw * kTileN * sizeof(float);
+    const size_t cap = pl.smem_bytes > 120 * 1024 ? (size_t)224 * 1024 : (size_t)113 * 1024;  // keep the CTAs-per-SM class
+    int st = pl.stages;
+    while (st > 2 && (size_t)st * stage + recv_bytes + 1024 > cap) --st;
+    const int keep = pl.stages;
+    pl.stages = st;
+    if ((size_t)st * stage + recv_bytes + 1024 <= cap && recv_fits(pl.splits)) {
+      pl.bulk = true;
+      pl.smem_bytes = (size_t)st * stage + recv_bytes + 1024;
+    } else {
+      pl.stages = keep;
+    }
+  }
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
@@ -772,6 +857,7 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
   p.cluster = pl.cluster ? 1 : 0;
+  p.bulk = pl.bulk ? 1 : 0;
   CUtensorMap tm_y;
   memset(&tm_y, 0, sizeof(tm_y));
   const size_t y_elt = pl.out_f32 ? 4 : 2;

@@ -149,6 +149,15 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t caddr, float a, float b, 
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+// Bulk asynchronous copy from this CTA's shared memory into a cluster partner's; the bytes
+// are counted on the partner's mbarrier (both destination operands are shared::cluster
+// addresses from cluster_map()).  16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_to_partner(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                     uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+               : "memory");
+}
 // Every thread of every CTA of the cluster arrives; hardware barrier, always reached.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
