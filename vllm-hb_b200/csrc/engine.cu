@@ -629,25 +629,70 @@ static int seq_ensure_block(hb_engine* e, hb_seq* s, int64_t pos) {
   return HB_OK;
 }
 
+// One row of a step: token `tok` of sequence `s` at position `pos`.  A decode step has one
+// row per sequence; a prefill chunk has consecutive positions of ONE sequence as its rows
+// (row i then attends to the keys of rows 0..i, which the same step wrote before its
+// attention kernel runs: causal attention over the growing cache, llama_tp.rs:313-316).
+struct StepRow {
+  hb_seq* s;
+  int64_t pos;
+  uint32_t tok;
+};
+
+static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tokens, float* logits_out,
+                    int logits_row0);
+
 static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t* tokens,
                        uint32_t* next_tokens, float* logits_out /* host [B, V] or null */) {
-  HB_CUDA_CHECK(cudaSetDevice(e->device));
   if (B <= 0 || B > e->max_batch)
     return fail(HB_ERR_INVALID_ARG, "batch %d outside [1, %d]", B, e->max_batch);
+  std::vector<StepRow> rows((size_t)B);
+  for (int b = 0; b < B; ++b) {
+    hb_seq* s = seqs[b];
+    if (!s) return fail(HB_ERR_INVALID_ARG, "null sequence at index %d", b);
+    for (int j = 0; j < b; ++j)
+      if (seqs[j] == s) return fail(HB_ERR_INVALID_ARG, "sequence repeated in one batch");
+    rows[b] = {s, s->len, tokens[b]};
+  }
+  int rc = run_rows(e, rows.data(), B, next_tokens, logits_out, 0);
+  if (rc) return rc;
+  for (int b = 0; b < B; ++b) seqs[b]->len += 1;
+  return HB_OK;
+}
+
+// Prefill of `n` prompt tokens of one sequence in chunks of up to max_batch rows; the
+// logits of the last token go to logits_out (host [V]) when it is not null.
+static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float* logits_out) {
+  std::vector<StepRow> rows;
+  size_t done = 0;
+  while (done < n) {
+    const int c = (int)std::min<size_t>(n - done, (size_t)e->max_batch);
+    rows.resize((size_t)c);
+    for (int i = 0; i < c; ++i) rows[i] = {s, s->len + i, ids[done + i]};
+    const bool last = done + (size_t)c == n;
+    int rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    if (rc) return rc;
+    s->len += c;
+    done += (size_t)c;
+  }
+  return HB_OK;
+}
+
+static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tokens, float* logits_out,
+                    int logits_row0) {
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
   int rc;
   uint32_t* h_ids = (uint32_t*)(e->h_inputs + e->off_ids);
   int32_t* h_pos = (int32_t*)(e->h_inputs + e->off_pos);
   int32_t* h_ctx = (int32_t*)(e->h_inputs + e->off_ctx);
   int64_t* h_slots = (int64_t*)(e->h_inputs + e->off_slots);
   int32_t* h_tables = (int32_t*)(e->h_inputs + e->off_tables);
+  for (int b = 0; b < B; ++b)
+    if ((rc = seq_ensure_block(e, rows[b].s, rows[b].pos))) return rc;
   for (int b = 0; b < B; ++b) {
-    hb_seq* s = seqs[b];
-    if (!s) return fail(HB_ERR_INVALID_ARG, "null sequence at index %d", b);
-    for (int j = 0; j < b; ++j)
-      if (seqs[j] == s) return fail(HB_ERR_INVALID_ARG, "sequence repeated in one batch");
-    const int64_t pos = s->len;
-    if ((rc = seq_ensure_block(e, s, pos))) return rc;
-    h_ids[b] = tokens[b];
+    hb_seq* s = rows[b].s;
+    const int64_t pos = rows[b].pos;
+    h_ids[b] = rows[b].tok;
     h_pos[b] = (int32_t)pos;
     h_ctx[b] = (int32_t)(pos + 1);
     h_slots[b] = s->blocks[pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + pos % HB_BLOCK_SIZE;
@@ -682,7 +727,8 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
   }
   HB_CUDA_CHECK(cudaMemcpyAsync(e->h_next, e->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, e->stream));
   if (logits_out)
-    HB_CUDA_CHECK(cudaMemcpyAsync(logits_out, e->d_logits, (size_t)B * e->V * 4, cudaMemcpyDeviceToHost, e->stream));
+    HB_CUDA_CHECK(cudaMemcpyAsync(logits_out, e->d_logits + (size_t)logits_row0 * e->V,
+                                  (size_t)(B - logits_row0) * e->V * 4, cudaMemcpyDeviceToHost, e->stream));
   int h_err = 0;
   HB_CUDA_CHECK(cudaMemcpyAsync(&h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
   HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
@@ -705,10 +751,8 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
     const int stw = hb_world_status(e->world);
     if (stw) return fail(stw, "a peer did not arrive in the all-reduce of the decode step");
   }
-  for (int b = 0; b < B; ++b) {
-    seqs[b]->len += 1;
+  for (int b = 0; b < B; ++b)
     if (next_tokens) next_tokens[b] = e->h_next[b];
-  }
   return HB_OK;
 }
 
@@ -1014,11 +1058,20 @@ int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t se
   if ((int64_t)seq_pos != s->len)
     return hb::fail(HB_ERR_INVALID_ARG, "hb_forward: seq_pos %zu but the sequence holds %lld tokens",
                     seq_pos, (long long)s->len);
-  // Prefill is fed token by token through the decode step: causal attention over the
-  // growing cache equals the masked prefill of llama_tp.rs:313-316.
-  for (size_t i = 0; i < n; ++i) {
-    hb_seq* one[1] = {s};
-    int rc = hb::decode_step(e, one, 1, ids + i, nullptr, i + 1 == n ? logits_out : nullptr);
+  // Prefill runs through the decode kernels in chunks whose rows are consecutive positions
+  // of this sequence: causal attention over the growing cache equals the masked prefill of
+  // llama_tp.rs:313-316.  (The optional in-attention RoPE appends one token per CTA, which a
+  // chunk cannot use: token by token then.)
+  if (e->fuse_rope) {
+    for (size_t i = 0; i < n; ++i) {
+      hb_seq* one[1] = {s};
+      int rc = hb::decode_step(e, one, 1, ids + i, nullptr, i + 1 == n ? logits_out : nullptr);
+      if (rc) return rc;
+    }
+    return HB_OK;
+  }
+  {
+    int rc = hb::prefill(e, s, ids, n, logits_out);
     if (rc) return rc;
   }
   return HB_OK;
