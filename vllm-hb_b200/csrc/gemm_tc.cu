@@ -37,8 +37,6 @@ struct TcParams {
   int epilogue, out_f32;
   int64_t ldy;
   int up_row_offset;        // SwiGLU: first row of the up projection inside W
-  int packed;               // weights stored tile-major: [n_tile][k_chunk][128][64]
-  int stagger;              // rotate the K walk per tile
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
   int bulk;                 // cluster exchange by bulk copies into a dedicated receive area
   int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
@@ -186,16 +184,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t full = smem_u32(&s_full[i]);
         const uint32_t sa = smem_base + i * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
-        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
-        const int kx = (kc0 + ci) * kTileK;
-        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + ci) * kTileN, full);
-        else tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
+        const int kx = (kc0 + i) * kTileK;
+        tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
         if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i) {
-        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
-        tma_load_2d(smem_base + i * stage_bytes + a_bytes * n_acc, &tm_x, (kc0 + ci) * kTileK, m_tile * p.m_pad,
+        tma_load_2d(smem_base + i * stage_bytes + a_bytes * n_acc, &tm_x, (kc0 + i) * kTileK, m_tile * p.m_pad,
                     smem_u32(&s_full[i]));
       }
       armed = pre;
@@ -206,10 +201,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t full = smem_u32(&s_full[s]);
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
-        const int ci = p.stagger ? (i + tile * 5) % n_kc : i;
-        const int kx = (kc0 + ci) * kTileK;
-        if (p.packed) tma_load_2d(sa, &tm_w, 0, (tile * p.k_chunks + kc0 + ci) * kTileN, full);
-        else tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
+        const int kx = (kc0 + i) * kTileK;
+        tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
         if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
         tma_load_2d(sa + a_bytes * n_acc, &tm_x, kx, m_tile * p.m_pad, full);
         armed = i + 1;
@@ -829,8 +822,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
       dev_done[cur] = true;
     }
   }
-  if (getenv("HB_TC_PACKED")) rc = encode_map(&pl.tm_w, W, N * (K / kTileK), kTileK, kTileN);  // speed experiment
-  else rc = encode_map(&pl.tm_w, W, N, K, kTileN);
+  rc = encode_map(&pl.tm_w, W, N, K, kTileN);
   if (rc) return rc;
   rc = encode_map(&pl.tm_x, X, M, K, pl.m_pad);
   return rc;
@@ -850,7 +842,6 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.epilogue = pl.epilogue; p.out_f32 = pl.out_f32 ? 1 : 0;
   p.ldy = ldy;
   p.up_row_offset = (int)pl.N;
-  p.packed = getenv("HB_TC_PACKED") ? 1 : 0;
   p.Y = Y;
   // counters first (16-byte aligned block), partials after
   p.counters = (int*)workspace;
@@ -892,7 +883,6 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
     p.rs_inv_n = 1.0f / link->n;
     p.rs_eps = link->eps;
   }
-  { const char* sg = getenv("HB_TC_STAGGER"); p.stagger = (sg && sg[0] == '1') ? 1 : 0; }  // measured: no gain, off
   dim3 grid((unsigned)(pl.n_tiles * pl.splits), (unsigned)pl.m_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
