@@ -297,7 +297,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         gemm_ms = prof.get("gemm", 0.0)
         achieved = gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else None
         # DRAM bytes (read + write) of the GEMM launches of one step, from the ncu captures
-        # summarised in profiles/gemm_tc_kernel_decode_shapes.md: per layer qkv 50.96 MB,
+        # (summaries are committed under profiles/): per layer qkv 50.96 MB,
         # o_proj 34.15, gate|up 239.4, down_proj 123.1, plus lm_head 1085.8.  Only the
         # full-size single-GPU workload was captured.
         traffic = None
