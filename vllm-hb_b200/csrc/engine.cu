@@ -572,16 +572,28 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     }
     // down( silu(gate x) * up x ) partial                     llama_tp.rs:333-339
     prof_mark(e, kCatGemmGateUp);
+    bool moe_scaled = false;
     if (e->use_tc && e->fused_swiglu) {
+      TcNormLink moe_link;
+      const TcGemmPlan& gpl = sp->layer[l * 4 + kGateUp];
+      static const bool moe_epi = [] { const char* v = getenv("HB_MOE_EPI"); return v && v[0] == '1'; }();
+      if (e->moe && moe_epi && gpl.tma_store && (gpl.cluster || gpl.splits == 1) && gpl.m_tiles == 1) {
+        // the routing weight of (token, expert) multiplies the expert's activations in the
+        // epilogue of the gate|up GEMM (expert = output tile / tiles per expert)
+        moe_link.post_scale = e->d_scale;
+        moe_link.post_groups = (int)e->E;
+        moe_link.post_tiles_per_group = (int)(e->I_l / 128);
+        moe_scaled = true;
+      }
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_act, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false,
-                         defer ? &consume : nullptr))) return rc;
+                         defer ? &consume : (moe_scaled ? &moe_link : nullptr)))) return rc;
     } else {
       if ((rc = run_gemm(e, sp, l, kGateUp, e->d_gu, e->d_x, w.wgu, B, 2 * e->I_e, e->H, false))) return rc;
       prof_mark(e, kCatOther);
       if ((rc = hb_silu_mul(st, e->d_act, e->d_gu, B, e->I_e, e->dtype))) return rc;
       ++e->last_launches;
     }
-    if (e->moe) {
+    if (e->moe && !moe_scaled) {
       // every expert ran on every token; the ones a token did not choose get weight 0,
       // the chosen ones their renormalised probability                 mixtral.rs:404-427
       prof_mark(e, kCatOther);

@@ -38,6 +38,10 @@ struct TcNormLink {
   int rowsq_tiles = 0;             // entries to sum per row = producer's N / 128
   int rowsq_stride = 0;
   float n = 1.f, eps = 0.f;        // mean over n features
+  // independent of the norm: scale of batch row m after the activation, per group of output
+  // tiles (mixture of experts: group = expert, post_scale[m * post_groups + group])
+  const float* post_scale = nullptr;
+  int post_groups = 0, post_tiles_per_group = 0;
 };
 
 // A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by

@@ -50,6 +50,10 @@ struct TcParams {
   const float* rowsq_in;
   int rowsq_stride, rowsq_tiles;
   float rs_inv_n, rs_eps;
+  // Mixture of experts: output tile t belongs to expert t / post_tiles_per_group; after the
+  // activation every batch row m is multiplied by post_scale[m * post_groups + expert].
+  const float* post_scale;
+  int post_groups, post_tiles_per_group;
   void* Y;
   float* partials;
   int* counters;
@@ -96,6 +100,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __shared__ __align__(8) uint64_t s_resid;  // residual tile landed (kEpiResidual)
   __shared__ __align__(8) uint64_t s_recv;   // partners' partials landed (bulk exchange)
   __shared__ float s_rscale[256];            // row scales of the deferred norm (consumer)
+  __shared__ float s_pscale[256];            // row scales applied after the activation (MoE weights)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool swiglu = p.epilogue == kEpiSwiGLU;
@@ -171,6 +176,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         sc = rsqrtf(a * p.rs_inv_n + p.rs_eps);
       }
       s_rscale[i] = sc;
+    }
+  }
+  if (warp >= 2 && p.post_scale) {
+    const int grp = (blockIdx.x / p.splits) / p.post_tiles_per_group;
+    for (int i = tid - 64; i < p.m_pad; i += 64) {
+      const int m = blockIdx.y * p.m_pad + i;
+      s_pscale[i] = m < p.M ? __ldcg(p.post_scale + (int64_t)m * p.post_groups + grp) : 0.f;
     }
   }
   if (warp == 0) {
@@ -411,6 +423,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = swiglu ? silu_f(g[j]) * u[j] : g[j];
+        if (p.post_scale) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] *= s_pscale[c0 + j];
+        }
         if (residual) {
           // h = resid + Y (both rounded to bf16 as the reference materialises them); the
           // norm weight is applied here, the row scale by the GEMM that consumes Y'
@@ -502,6 +518,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = silu_f(v[j]) * u[j];
+        }
+        if (p.post_scale) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] *= s_pscale[g * 16 + j];
         }
         uint8_t* dst = smem_gen + (uint32_t)(g - g0) * grp_bytes;
 #pragma unroll
@@ -873,6 +893,13 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
     p.norm_w = (const __nv_bfloat16*)link->norm_w;
     p.rowsq_out = link->rowsq_out;
     p.rowsq_stride = link->rowsq_stride;
+  }
+  if (link && link->post_scale) {
+    if (!p.tma_store || (pl.splits > 1 && !pl.cluster) || link->post_tiles_per_group < 1)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: post-activation row scaling needs the bulk-store epilogue");
+    p.post_scale = link->post_scale;
+    p.post_groups = link->post_groups;
+    p.post_tiles_per_group = link->post_tiles_per_group;
   }
   if (link && link->rowsq_in) {
     if (!p.tma_store || (pl.splits > 1 && !pl.cluster))
