@@ -12,6 +12,8 @@ norm weight ones, eps 1e-5; M in {1, 8, 64, 256}; (K, N) = (28672, 8192) (down_p
     unfused    hb_gemm -> hb_all_reduce (peer memory) -> hb_add_rms_norm
     baseline   torch.matmul (cuBLAS) -> NCCL all_reduce -> hb_add_rms_norm: the
                reference's sequence (src/engine/arch/llama_tp.rs:327,533-552)
+    baseline_eager  the same with the add and the norm as the reference ships them for bf16:
+               six eager elementwise launches (src/kernels/rms_norm.rs:128-132)
 Device time with CUDA events on the launching stream, max over ranks, weights rotated
 over 4 buffers so that they come from HBM, not L2.
 """
@@ -106,6 +108,14 @@ def main() -> None:
                 hb.check(hb.lib.hb_add_rms_norm(st, out[0].data_ptr(), out[1].data_ptr(), p2.data_ptr(), resid.data_ptr(),
                                                 nw.data_ptr(), M, N, 1e-5, hb.BF16))
 
+            def baseline_eager(i):
+                p2 = torch.matmul(x, ws[i].t())
+                if world > 1:
+                    dist.all_reduce(p2)
+                h = resid + p2
+                var = h.pow(2).mean(-1, keepdim=True) + 1e-5
+                out[0].copy_(h / var.sqrt() * nw)
+
             row = {"K": K, "N": N, "M": M, "tp": world}
             row["fused_auto_us"] = timed(fused(hb.ALGO_AUTO), 4)
             if world > 1:
@@ -115,6 +125,7 @@ def main() -> None:
                 row["gemm_arn_us"] = timed(gemm_arn, 4)
             row["unfused_us"] = timed(unfused, 4)
             row["baseline_cublas_nccl_us"] = timed(baseline, 4)
+            row["baseline_eager_norm_us"] = timed(baseline_eager, 4)
             hbm_bytes = 2 * (Kl * N + M * Kl + 3 * M * N + N)
             nvl_bytes = 2 * (world - 1) / world * 2 * M * N if world > 1 else 0
             row["hbm_bytes"], row["nvlink_bytes_per_dir"] = hbm_bytes, nvl_bytes

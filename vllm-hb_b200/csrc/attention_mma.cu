@@ -423,6 +423,8 @@ int paged_attention_mma_prepare() {
                                        (int)mma_attn_smem(4)));
     HB_CUDA_CHECK(cudaFuncSetAttribute(paged_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)mma_attn_smem(2)));
+    HB_CUDA_CHECK(cudaFuncSetAttribute(paged_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)mma_attn_smem(8)));
     done[dev] = true;
   }
   return HB_OK;
@@ -451,6 +453,14 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
   if (const char* ev = getenv("HB_ATTN_WARPS")) {  // experiment knob
     if (ev[0] == '2') nw = 2;
     if (ev[0] == '4') nw = 4;
+    if (ev[0] == '8') nw = 8;  // one CTA per SM with two warps per scheduler: for grids below the SM count
+  }
+  if (nw == 8) {
+    HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<8>, grid, dim3(256), mma_attn_smem(8), st, tm_k, tm_v,
+                             (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
+                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache)));
+    return HB_OK;
   }
   if (nw == 2) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
