@@ -576,7 +576,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if (e->use_tc && e->fused_swiglu) {
       TcNormLink moe_link;
       const TcGemmPlan& gpl = sp->layer[l * 4 + kGateUp];
-      static const bool moe_epi = [] { const char* v = getenv("HB_MOE_EPI"); return v && v[0] == '1'; }();
+      static const bool moe_epi = [] { const char* v = getenv("HB_MOE_EPI"); return !(v && v[0] == '0'); }();  // HB_MOE_EPI=0: separate kernel
       if (e->moe && moe_epi && gpl.tma_store && (gpl.cluster || gpl.splits == 1) && gpl.m_tiles == 1) {
         // the routing weight of (token, expert) multiplies the expert's activations in the
         // epilogue of the gate|up GEMM (expert = output tile / tiles per expert)
