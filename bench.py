@@ -271,7 +271,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     clocks = sampler.stop() if rank == 0 else None
     launches = eng.last_step_launches() * K
 
-    # per-kernel-kind device time of a few eager steps (CUDA events on the engine's stream)
+    # per-kernel-kind device time of a few profile steps (CUDA events between the kernels on the engine's stream)
     prof = {}
     for _ in range(args.profile_steps):
         nxt2, ms = eng.profile_step(seqs, nxt.copy())
@@ -320,7 +320,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
                          "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                          "frac": (achieved / peak) if achieved else None, "traffic": traffic,
                          "algorithmic_bytes_per_step": gemm_bytes, "ms_per_step": gemm_ms,
-                         "timing": "CUDA events between the kernels of eager (ungraphed) steps on the engine stream"},
+                         "timing": "CUDA events recorded between the kernels of profile steps on the engine stream (graph with event nodes)"},
             "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1e3) / 1e9,
                               "frac": step_bytes / (dev_ms / K / 1e3) / 1e9 / peak},
             "kernel_ms_per_step": prof,

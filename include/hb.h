@@ -411,8 +411,10 @@ int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t se
  * [B, vocab]) may be NULL.  Copies in and out happen inside the call. */
 int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,
                     uint32_t* next_tokens, float* logits_opt);
-/* One decode step issued kernel by kernel (no graph) with CUDA events between the
- * kernels: ms_by_kind receives HB_PROFILE_KINDS floats = device time spent in
+/* One decode step with CUDA events between its kernels — captured into a graph with an
+ * event-record node after every kernel and replayed, so the kernels run back to back as in
+ * a normal step (HB_PROFILE_EAGER=1 or HB_NO_GRAPH=1: issued kernel by kernel on the
+ * stream): ms_by_kind receives HB_PROFILE_KINDS floats = device time spent in
  * 0 QKV projection, 1 decode attention, 2 RoPE + KV write, 3 (add +) RMSNorm, 4 embedding /
  * argmax / SwiGLU gate, 5 all-reduce, 6 o_proj, 7 gate|up projection, 8 down_proj,
  * 9 lm_head (6 and 8 include the fused all-reduce + residual + norm when that kernel

@@ -121,6 +121,7 @@ struct hb_engine {
   int64_t last_launches = 0;
   // per-kernel-kind timing of one eager step (hb_engine_profile_step)
   bool profiling = false;
+  bool prof_capture = false;  // the profiled step is being captured: events become graph nodes
   std::vector<cudaEvent_t> prof_events;
   std::vector<int> prof_cats;
   size_t prof_used = 0;
@@ -473,7 +474,8 @@ static void prof_mark(hb_engine* e, int cat) {
     cudaEventCreate(&ev);
     e->prof_events.push_back(ev);
   }
-  cudaEventRecord(e->prof_events[e->prof_used++], e->stream);
+  if (e->prof_capture) cudaEventRecordWithFlags(e->prof_events[e->prof_used++], e->stream, cudaEventRecordExternal);
+  else cudaEventRecord(e->prof_events[e->prof_used++], e->stream);
   e->prof_cats.push_back(cat);
 }
 
@@ -733,9 +735,38 @@ static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tok
     HB_CUDA_CHECK(cudaGraphLaunch(sp->graph, e->stream));
     HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
   } else {
-    HB_CUDA_CHECK(cudaEventRecord(e->ev0, e->stream));
-    if ((rc = issue_step(e, sp, B))) return rc;
-    HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
+    // Profiling.  With graphs enabled the step is captured once more with an event-record
+    // node between the kernels and replayed, so that the per-kind times are those of the
+    // kernels inside a graph (HB_PROFILE_EAGER=1, or a failed capture: kernel by kernel
+    // on the stream, which adds the launch gaps).
+    static const bool eager_only = [] { const char* v = getenv("HB_PROFILE_EAGER"); return v && v[0] == '1'; }();
+    bool done = false;
+    if (e->profiling && e->use_graph && !eager_only) {
+      cudaGraph_t g = nullptr;
+      cudaGraphExec_t ge = nullptr;
+      if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        e->prof_capture = true;
+        rc = issue_step(e, sp, B);
+        e->prof_capture = false;
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+        if (!rc && ce == cudaSuccess && cudaGraphInstantiate(&ge, g, 0) == cudaSuccess) {
+          HB_CUDA_CHECK(cudaEventRecord(e->ev0, e->stream));
+          ce = cudaGraphLaunch(ge, e->stream);
+          HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
+          HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
+          done = ce == cudaSuccess;
+        }
+        if (ge) cudaGraphExecDestroy(ge);
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+      }
+      if (!done) { e->prof_used = 0; e->prof_cats.clear(); }
+    }
+    if (!done) {
+      HB_CUDA_CHECK(cudaEventRecord(e->ev0, e->stream));
+      if ((rc = issue_step(e, sp, B))) return rc;
+      HB_CUDA_CHECK(cudaEventRecord(e->ev1, e->stream));
+    }
   }
   HB_CUDA_CHECK(cudaMemcpyAsync(e->h_next, e->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, e->stream));
   if (logits_out)
