@@ -279,6 +279,13 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         for k, v in ms.items():
             prof[k] = prof.get(k, 0.0) + v / args.profile_steps
 
+    # the exchange kernels also hold a rank until its slowest peer arrives: keep every rank's share
+    prof_ranks = None
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, {k: round(v, 4) for k, v in prof.items()})
+        prof_ranks = {k: [g.get(k, 0.0) for g in gathered] for k in ("all_reduce", "gemm", "attention")}
+
     ctx_mid = [P + W + K // 2 + 1] * B
     step_bytes = eng.step_bytes(ctx_mid)
     gemm_bytes = eng.gemm_bytes(B)
@@ -324,6 +331,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1e3) / 1e9,
                               "frac": step_bytes / (dev_ms / K / 1e3) / 1e9 / peak},
             "kernel_ms_per_step": prof,
+            "kernel_ms_per_step_by_rank": prof_ranks,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline and args.workload == "auto":

@@ -23,7 +23,8 @@ from typing import Optional, Sequence
 import numpy as np
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libhb.so"
+# HB_LIBRARY names another build of the same library (the trace variant, libhb_trace.so)
+LIB_PATH = Path(os.environ["HB_LIBRARY"]).resolve() if os.environ.get("HB_LIBRARY") else _HERE / "libhb.so"
 
 if not LIB_PATH.exists():
     raise ImportError(
