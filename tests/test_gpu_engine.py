@@ -180,6 +180,38 @@ def test_random_init_bf16_tensor_core_path(hb, cuda, norm_ones, fused, monkeypat
     eng.close()
 
 
+@pytest.mark.parametrize("B", [1, 16, 48])
+def test_rope_epilogue_matches_separate_kernel(hb, cuda, B, monkeypatch):
+    """RoPE and the paged KV write in the epilogue of the q|k|v GEMM (the default when a
+    head is one output tile) against the separate RoPE + KV kernel (HB_ROPE_EPI=0): the
+    roundings fall in the same places, so logits and tokens are identical bit for bit."""
+    outs = []
+    for mode in ("1", "0"):
+        monkeypatch.setenv("HB_ROPE_EPI", mode)
+        eng = hb.Engine.create_random(SHAPE_TC128, seed=3, std=0.02, norm_ones=False, max_seq_len=64,
+                                      bf16=True, max_batch=B)
+        rng = np.random.default_rng(1)
+        prompts = rng.integers(0, SHAPE_TC128["vocab_size"], size=(B, 24)).astype(np.uint32)
+        seqs = [eng.create_kv_cache() for _ in range(B)]
+        logits = np.empty((B, SHAPE_TC128["vocab_size"]), dtype=np.float32)
+        got = []
+        for t in range(24):
+            tok = eng.decode_batch(seqs, prompts[:, t], logits=logits)
+            got.append((tok.copy(), logits.copy()))
+        launches = eng.last_step_launches()
+        # a prompt through the chunked prefill path as well
+        seq2 = eng.create_kv_cache()
+        pre = eng.forward_with_cache(prompts[0].tolist(), 0, seq2)
+        outs.append((got, launches, np.asarray(pre).copy()))
+        eng.close()
+    (a, la, pa), (b, lb, pb) = outs
+    assert la < lb  # one launch per layer less, one table kernel more
+    for (ta, xa), (tb, xb) in zip(a, b):
+        assert np.array_equal(ta, tb)
+        assert np.array_equal(xa, xb)
+    assert np.array_equal(pa, pb)
+
+
 def test_step_bytes_formula(hb, cuda):
     eng = hb.Engine.create_random(SHAPE_TC, max_seq_len=64, bf16=True, max_batch=4)
     H, I, L, V, hd, hq, hkv = 512, 1024, 2, 2048, 64, 8, 2

@@ -122,6 +122,12 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// One RoPE pair (x1, x2) = (element i, element i + head_dim/2) rotated by (c, s); every
+// kernel that rotates uses this one expression so that they agree bit for bit.
+__device__ __forceinline__ void rope_rotate(float x1, float x2, float c, float s, float* o1, float* o2) {
+  *o1 = x1 * c - x2 * s;
+  *o2 = x1 * s + x2 * c;
+}
 // Sum over the whole block; every thread gets the total. `smem` holds >= 33 floats.
 __device__ __forceinline__ float block_sum(float v, float* smem) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;

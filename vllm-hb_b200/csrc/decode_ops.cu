@@ -50,9 +50,7 @@ rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
     b.unpack(x2);
 #pragma unroll
     for (int j = 0; j < N; ++j) {
-      const float c = s_cos[v * N + j], s = s_sin[v * N + j];
-      o1[j] = x1[j] * c - x2[j] * s;
-      o2[j] = x1[j] * s + x2[j] * c;
+      rope_rotate(x1[j], x2[j], s_cos[v * N + j], s_sin[v * N + j], &o1[j], &o2[j]);
     }
     a.pack(o1);
     b.pack(o2);
@@ -91,6 +89,34 @@ int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
     HB_CUDA_CHECK(launch_pdl(rope_kv_kernel<T>, dim3((unsigned)n_tokens), dim3(kRkThreads), 0, st, (T*)qkv,
                              (T*)k_cache, (T*)v_cache, positions, slot_mapping, inv_freq, n_q_heads, n_kv_heads,
                              head_dim, num_blocks));
+  });
+  return HB_OK;
+}
+
+// (cos, sin) of position[t] * inv_freq[i], rounded to T like rope_kv_kernel rounds them:
+// computed once per decode step for the GEMM epilogue that rotates q and k (TcNormLink).
+template <typename T>
+__global__ void rope_table_kernel(float2* __restrict__ table, const int32_t* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int64_t n_tokens, int half) {
+  pdl_trigger();
+  pdl_grid_wait();
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * half) return;
+  const int64_t t = idx / half;
+  const int i = (int)(idx % half);
+  float s, c;
+  sincosf((float)positions[t] * inv_freq[i], &s, &c);
+  table[idx] = make_float2(to_f32<T>(from_f32<T>(c)), to_f32<T>(from_f32<T>(s)));
+}
+
+int rope_table(cudaStream_t st, float2* table, const int32_t* positions, const float* inv_freq,
+               int64_t n_tokens, int head_dim, hb_dtype dtype) {
+  if (n_tokens == 0) return HB_OK;
+  const int half = head_dim / 2;
+  const int64_t total = n_tokens * half;
+  HB_DISPATCH_DTYPE(dtype, T, {
+    HB_CUDA_CHECK(launch_pdl(rope_table_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, table,
+                             positions, inv_freq, n_tokens, half));
   });
   return HB_OK;
 }

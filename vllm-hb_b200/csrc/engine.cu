@@ -59,6 +59,7 @@ struct StepPlans {
   TcGemmPlan lm_head;
   int attn_splits = 1;
   bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
+  bool rope_epi = false;    // RoPE + KV write folded into the q|k|v GEMM epilogue (TcNormLink)
   int64_t launches = 0;  // kernels in one step (fixed per batch size)
   cudaGraphExec_t graph = nullptr;
 };
@@ -81,6 +82,7 @@ struct hb_engine {
   bool moe = false;
   float* d_scale = nullptr;  // [max_batch, E] routing weights of the step
   float* d_rowsq = nullptr;  // [max_batch, rowsq_stride] row sums of the deferred norm
+  float2* d_rope_cs = nullptr;  // [max_batch, hd/2] (cos, sin) of the step's positions
   int rowsq_stride = 0;
   // weights
   void* embed = nullptr;
@@ -334,6 +336,7 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   e->rowsq_stride = (int)(((e->H + 127) / 128 + 3) / 4 * 4);
   if ((rc = dev_alloc(e, (void**)&e->d_rowsq, (size_t)B * e->rowsq_stride * 4))) return rc;
   HB_CUDA_CHECK(cudaMemset(e->d_rowsq, 0, (size_t)B * e->rowsq_stride * 4));
+  if ((rc = dev_alloc(e, (void**)&e->d_rope_cs, (size_t)B * (e->hd / 2 + 1) * sizeof(float2)))) return rc;
   if ((rc = dev_alloc(e, &e->d_proj, (size_t)B * e->H * es))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_logits, (size_t)B * e->V * 4))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_next, (size_t)B * 4))) return rc;
@@ -420,6 +423,12 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
     }
     if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
     ws = std::max(ws, sp.lm_head.workspace_bytes());
+    // RoPE and the KV write ride in the q|k|v GEMM epilogue when its output tile is one head
+    // (HB_ROPE_EPI=0: the separate kernel)
+    const char* re_env = getenv("HB_ROPE_EPI");  // read per plan, so that tests can compare both forms
+    const bool no_rope_epi = re_env && re_env[0] == '0';
+    sp.rope_epi = !no_rope_epi && !e->fuse_rope && e->dtype == HB_BF16 && e->hd == 128 && e->L > 0 &&
+                  gemm_tc_rope_epilogue_ok(sp.layer[kQkv]);
     if (sp.defer_norm) {
       auto can_scale = [](const TcGemmPlan& pl) { return pl.tma_store && (pl.cluster || pl.splits == 1) && pl.m_tiles == 1; };
       bool ok = can_scale(sp.lm_head);
@@ -529,14 +538,33 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   consume.rowsq_stride = e->rowsq_stride;
   consume.n = (float)e->H;
   consume.eps = eps;
+  const bool rope_epi = e->use_tc && sp->rope_epi;
+  if (rope_epi) {
+    // the step's (cos, sin) table, shared by the q|k|v epilogues of every layer
+    prof_mark(e, kCatRopeKv);
+    if ((rc = rope_table(st, e->d_rope_cs, d_pos, e->d_inv_freq, B, (int)e->hd, e->dtype))) return rc;
+    ++e->last_launches;
+  }
   for (int64_t l = 0; l < e->L; ++l) {
     auto& w = e->layers[l];
     // q|k|v = x . Wqkv^T                                      llama_tp.rs:232-234
     prof_mark(e, kCatGemm);
+    TcNormLink qkv_link;
+    if (defer && l > 0) qkv_link = consume;
+    if (rope_epi) {
+      // RoPE + KV append in the epilogue                      llama_tp.rs:242-259
+      qkv_link.rope_cs = e->d_rope_cs;
+      qkv_link.kv_slots = d_slots;
+      qkv_link.k_cache = e->kc[l];
+      qkv_link.v_cache = e->vc[l];
+      qkv_link.n_q_heads = (int)e->hq_l;
+      qkv_link.n_kv_heads = (int)e->hkv_l;
+      qkv_link.num_blocks = e->num_blocks;
+    }
     if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false,
-                       (defer && l > 0) ? &consume : nullptr))) return rc;
+                       ((defer && l > 0) || rope_epi) ? &qkv_link : nullptr))) return rc;
     // RoPE + KV append                                        llama_tp.rs:242-259
-    if (!e->fuse_rope) {
+    if (!e->fuse_rope && !rope_epi) {
       prof_mark(e, kCatRopeKv);
       if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
                               (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;

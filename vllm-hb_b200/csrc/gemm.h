@@ -42,6 +42,18 @@ struct TcNormLink {
   // tiles (mixture of experts: group = expert, post_scale[m * post_groups + group])
   const float* post_scale = nullptr;
   int post_groups = 0, post_tiles_per_group = 0;
+  // independent of the norm: RoPE and the paged KV write in the epilogue of the q|k|v
+  // projection (cluster plans, bf16, head_dim 128 so that an output tile is one head).
+  // Query heads are rotated and stored to Y as usual; key heads are rotated and written to
+  // slot kv_slots[m] of k_cache, value heads copied to v_cache, and neither is stored to Y.
+  // rope_cs[m * 64 + i] = (cos, sin) of row m's position times frequency i, rounded to bf16
+  // (rope_table() in ops.h); caches are [num_blocks, n_kv_heads, 16, 128].
+  const float2* rope_cs = nullptr;
+  const int64_t* kv_slots = nullptr;
+  void* k_cache = nullptr;
+  void* v_cache = nullptr;
+  int n_q_heads = 0, n_kv_heads = 0;
+  int64_t num_blocks = 0;
 };
 
 // A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by
@@ -74,6 +86,8 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
                  int epilogue, bool out_f32, int device, int force_splits = 0);
 // Y row stride ldy in elements.  workspace: plan.workspace_bytes(), zeroed once.
 // err_flag (device int, may be null) is set non-zero when a bounded wait ran out.
+// True when `plan` can carry the RoPE + KV-write epilogue of TcNormLink.
+bool gemm_tc_rope_epilogue_ok(const TcGemmPlan& plan);
 int gemm_tc_run(const TcGemmPlan& plan, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
                 int* err_flag, const TcNormLink* link = nullptr);
 

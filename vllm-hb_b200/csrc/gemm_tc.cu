@@ -54,6 +54,13 @@ struct TcParams {
   // activation every batch row m is multiplied by post_scale[m * post_groups + expert].
   const float* post_scale;
   int post_groups, post_tiles_per_group;
+  // RoPE + paged KV write (see TcNormLink): tile t is head t of the [q|k|v] row.
+  const float2* rope_cs;
+  const int64_t* kv_slots;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  int rope_nq, rope_nkv;
+  int64_t kv_num_blocks;
   void* Y;
   float* partials;
   int* counters;
@@ -477,7 +484,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (lane == 0 && m < p.M) p.rowsq_out[(int64_t)m * p.rowsq_stride + tile] = ss;
       }
     }
-    if (tail_ok && tid == 0 && m_base + split * CW < p.M) {
+    bool store_y = true;
+    if (p.rope_cs) {
+      // the staged tile is one head for this CTA's CW batch rows: rotate query and key heads
+      // (pairs (i, i + 64), values as rounded to bf16 above), send key and value heads
+      // straight to their cache slots
+      __nv_bfloat16* ts = reinterpret_cast<__nv_bfloat16*>(smem_gen + out_off);
+      const int head = tile, row0 = m_base + split * CW;
+      if (tail_ok && head < p.rope_nq + p.rope_nkv) {
+        for (int idx = tid; idx < CW * 64; idx += kTcThreads) {
+          const int cl = idx >> 6, i = idx & 63, m = row0 + cl;
+          if (m < p.M) {
+            const float2 cs = __ldg(p.rope_cs + (int64_t)m * 64 + i);
+            const float x1 = __bfloat162float(ts[cl * kTileN + i]), x2 = __bfloat162float(ts[cl * kTileN + 64 + i]);
+            float o1, o2;
+            rope_rotate(x1, x2, cs.x, cs.y, &o1, &o2);
+            ts[cl * kTileN + i] = __float2bfloat16_rn(o1);
+            ts[cl * kTileN + 64 + i] = __float2bfloat16_rn(o2);
+          }
+        }
+      }
+      if (head < p.rope_nq) fence_async_smem();
+      __syncthreads();
+      if (head >= p.rope_nq) {
+        store_y = false;
+        if (tail_ok) {
+          const bool is_k = head < p.rope_nq + p.rope_nkv;
+          __nv_bfloat16* cache = is_k ? p.k_cache : p.v_cache;
+          const int kvh = head - p.rope_nq - (is_k ? 0 : p.rope_nkv);
+          for (int idx = tid; idx < CW * 16; idx += kTcThreads) {
+            const int cl = idx >> 4, v = idx & 15, m = row0 + cl;
+            if (m < p.M) {
+              const int64_t slot = __ldg(p.kv_slots + m);
+              if (slot >= 0 && slot < p.kv_num_blocks * HB_BLOCK_SIZE) {
+                const int64_t blk = slot / HB_BLOCK_SIZE, off = slot % HB_BLOCK_SIZE;
+                __nv_bfloat16* dst = cache + ((blk * p.rope_nkv + kvh) * HB_BLOCK_SIZE + off) * (int64_t)kTileN;
+                reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(ts + cl * kTileN)[v];
+              }
+            }
+          }
+        }
+      }
+    }
+    if (tail_ok && store_y && tid == 0 && m_base + split * CW < p.M) {
       tma_store_2d(&tm_y, smem_base + out_off, tile * kTileN, m_base + split * CW);
       if (residual) tma_store_2d(&tm_h, smem_base + h_off, tile * kTileN, m_base + split * CW);
       tma_store_commit();
@@ -848,6 +897,11 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   return rc;
 }
 
+bool gemm_tc_rope_epilogue_ok(const TcGemmPlan& pl) {
+  return pl.cluster && pl.splits > 1 && pl.tma_store && !pl.out_f32 && pl.epilogue == kEpiStore &&
+         pl.N % kTileN == 0;
+}
+
 int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
                 int* err_flag, const TcNormLink* link) {
   if (pl.splits > 1 && !pl.cluster && !workspace)
@@ -900,6 +954,18 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
     p.post_scale = link->post_scale;
     p.post_groups = link->post_groups;
     p.post_tiles_per_group = link->post_tiles_per_group;
+  }
+  if (link && link->rope_cs) {
+    if (!gemm_tc_rope_epilogue_ok(pl) || !p.tma_store || !link->kv_slots || !link->k_cache || !link->v_cache ||
+        pl.N != (int64_t)(link->n_q_heads + 2 * link->n_kv_heads) * kTileN)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the RoPE epilogue needs a cluster plan over [q|k|v] heads of 128");
+    p.rope_cs = link->rope_cs;
+    p.kv_slots = link->kv_slots;
+    p.k_cache = (__nv_bfloat16*)link->k_cache;
+    p.v_cache = (__nv_bfloat16*)link->v_cache;
+    p.rope_nq = link->n_q_heads;
+    p.rope_nkv = link->n_kv_heads;
+    p.kv_num_blocks = link->num_blocks;
   }
   if (link && link->rowsq_in) {
     if (!p.tma_store || (pl.splits > 1 && !pl.cluster))

@@ -33,6 +33,11 @@ int rope_kv_write(cudaStream_t st, void* qkv, void* k_cache, void* v_cache,
                   int64_t n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                   int64_t num_blocks, hb_dtype dtype);
 
+// table[t * head_dim/2 + i] = (cos, sin) of positions[t] * inv_freq[i], rounded to `dtype`
+// as rope_kv_write rounds them (consumed by the GEMM epilogue that rotates q and k).
+int rope_table(cudaStream_t st, float2* table, const int32_t* positions, const float* inv_freq,
+               int64_t n_tokens, int head_dim, hb_dtype dtype);
+
 // Fill a [rows, cols] slice of a global [g_rows, g_cols] tensor with N(0, std) drawn
 // from a counter-based generator keyed by (seed, tensor id, global element index).
 int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
