@@ -274,6 +274,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     # per-kernel-kind device time of a few profile steps (CUDA events between the kernels on the engine's stream)
     prof = {}
     for _ in range(args.profile_steps):
+        barrier()  # ranks enter together: a rank that arrives early books the wait as exchange time
         nxt2, ms = eng.profile_step(seqs, nxt.copy())
         nxt = nxt2
         for k, v in ms.items():
