@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -65,6 +66,7 @@ struct TcParams {
   float* partials;
   int* counters;
   int* err_flag;
+  int trace_id;             // trace build only: slot of this launch in the launch ring
 };
 
 // Optional phase timestamps (compiled in with -DHB_TC_TRACE only): every CTA records
@@ -88,8 +90,26 @@ __device__ __forceinline__ void tc_trace(int slot) {
   if (slot == 7) g_tc_trace[cta * kTraceSlots + 15] = (unsigned long long)clock64();
 }
 #define TC_TRACE(cond, slot) do { if (cond) tc_trace(slot); } while (0)
+// One record per launch (slot = launch number at issue time, so the launches of a replayed
+// graph keep their slots): start of CTA (0,0), latest exit of any CTA, N and K.
+constexpr int kLaunchRing = 1024;
+static __device__ unsigned long long g_tc_launch[kLaunchRing * 4];
+// what: 0 = kernel entry, 1 = exit, 3 = the producer thread has passed its dependency wait
+// (the previous kernel of the stream has completed)
+__device__ __forceinline__ void tc_launch_trace(int id, int what, int n, int k) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  if (what == 1) {
+    atomicMax(&g_tc_launch[id * 4 + 1], t);
+  } else if (blockIdx.x == 0 && blockIdx.y == 0) {
+    g_tc_launch[id * 4 + what] = t;
+    if (what == 0) g_tc_launch[id * 4 + 2] = ((unsigned long long)(unsigned)n << 32) | (unsigned)k;
+  }
+}
+#define TC_LAUNCH_TRACE(what) do { if (tid == 0) tc_launch_trace(p.trace_id, what, p.N, p.k_chunks * kTileK); } while (0)
 #else
 #define TC_TRACE(cond, slot) do { } while (0)
+#define TC_LAUNCH_TRACE(what) do { } while (0)
 #endif
 
 // ----------------------------------------------------------------------- kernel
@@ -113,6 +133,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const bool swiglu = p.epilogue == kEpiSwiGLU;
   const int n_acc = swiglu ? 2 : 1;
   TC_TRACE(tid == 0, 0);
+  TC_LAUNCH_TRACE(0);
 
   // work unit: blockIdx.x = tile * splits + split, blockIdx.y = batch tile
   const int tile = blockIdx.x / p.splits;
@@ -208,6 +229,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
       }
       pdl_wait();
+      TC_LAUNCH_TRACE(3);
       for (int i = 0; i < pre; ++i) {
         tma_load_2d(smem_base + i * stage_bytes + a_bytes * n_acc, &tm_x, (kc0 + i) * kTileK, m_tile * p.m_pad,
                     smem_u32(&s_full[i]));
@@ -671,6 +693,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   TC_TRACE(tid == 0, 7);
+  TC_LAUNCH_TRACE(1);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)p.tmem_cols)
@@ -758,8 +781,9 @@ static bool bulk_exchange_enabled() {
 }
 
 static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
-  int s = 1;
-  while (s < 8 && units * s < sm_count && k_chunks / (s * 2) >= 4) s *= 2;
+  int s = 1, cap = 8;
+  if (const char* ev = getenv("HB_TC_MAX_SPLITS")) cap = std::max(1, atoi(ev));  // experiment knob
+  while (s < cap && units * s < sm_count && k_chunks / (s * 2) >= 4) s *= 2;
   return s;
 }
 
@@ -909,6 +933,10 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
                 pl.workspace_bytes());
   TcParams p;
   memset(&p, 0, sizeof(p));
+#ifdef HB_TC_TRACE
+  static std::atomic<int> launch_no{0};
+  p.trace_id = launch_no.fetch_add(1) % kLaunchRing;
+#endif
   p.M = (int)pl.M; p.N = (int)pl.N;
   p.m_pad = pl.m_pad; p.splits = pl.splits; p.stages = pl.stages; p.tmem_cols = pl.tmem_cols;
   p.k_chunks = (int)(pl.K / kTileK);
@@ -1006,6 +1034,11 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
 }  // namespace hb
 
 #ifdef HB_TC_TRACE
+extern "C" int hb_debug_tc_launches(unsigned long long* host_out, int n) {
+  if (n > hb::kLaunchRing) n = hb::kLaunchRing;
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host_out, hb::g_tc_launch, sizeof(unsigned long long) * n * 4);
+}
 extern "C" int hb_debug_tc_trace(unsigned long long* host_out, int n_ctas) {
   if (n_ctas > hb::kTraceCtas) n_ctas = hb::kTraceCtas;
   cudaDeviceSynchronize();
