@@ -69,10 +69,15 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                       const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens, int hq,
                       int hkv, int nrep, int64_t max_blocks, int64_t num_blocks, int n_splits, float scale,
                       int64_t q_stride, int window, int* err_flag, const float* __restrict__ rope_inv_freq,
-                      __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
+                      __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int fresh) {
   constexpr int kMmaAttnWarps = NW, kMmaAttnThreads = NW * 32;
   pdl_trigger();
-  pdl_grid_wait();
+  // fresh >= 0: at most `fresh` tokens at the end of every sequence were written by the
+  // kernels right before this one (the current step's K/V); every earlier block of the pool
+  // is final, so its copies may start before those kernels have completed.  The context
+  // lengths and block tables are step inputs, not products of a kernel.
+  const bool early = fresh >= 0 && rope_inv_freq == nullptr;
+  if (!early) pdl_grid_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kMmaAttnWarps][kAttnStages];
   __shared__ int s_abort;
@@ -141,6 +146,46 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   }
   __syncthreads();
 
+  // ---- block table entries of this warp, 32 at a time, one per lane
+  const int32_t* table = block_tables + seq * max_blocks;
+  int tab_base = 0;
+  int32_t tab = 0;
+  auto load_tab = [&](int base) {
+    tab_base = base;
+    const int i = base + lane;
+    tab = i < n_w ? table[b0 + warp + kMmaAttnWarps * i] : 0;
+  };
+  // Whole warp calls; lane 0 issues block i of this warp into stage i % kAttnStages.
+  auto issue = [&](int i) {
+    if (i >= tab_base + 32) load_tab(i);
+    int64_t phys = __shfl_sync(0xffffffffu, tab, i - tab_base);
+    if (phys < 0 || phys >= num_blocks) phys = 0;  // never read outside the pool
+    if (lane == 0) {
+      const int s = i % kAttnStages;
+      const uint32_t bar = smem_u32(&s_full[warp][s]);
+      const uint32_t dst = ring + (uint32_t)s * kAttnStageBytes;
+      const int row = (int)((phys * hkv + kvh) * HB_BLOCK_SIZE);
+      mbar_expect_tx(bar, kAttnStageBytes);
+      tma_load_2d(dst, &tm_k, 0, row, bar);
+      tma_load_2d(dst + 2048, &tm_k, 64, row, bar);
+      tma_load_2d(dst + 4096, &tm_v, 0, row, bar);
+      tma_load_2d(dst + 6144, &tm_v, 64, row, bar);
+    }
+  };
+  load_tab(0);
+  int issued = 0;
+  if (early) {
+    // blocks [0, stable) were complete before this step began
+    const int stable = max(0, ctx - fresh) / HB_BLOCK_SIZE;
+    for (; issued < min(kAttnStages, n_w); ++issued) {
+      if (b0 + warp + kMmaAttnWarps * issued >= stable) break;
+      issue(issued);
+    }
+    pdl_grid_wait();
+  }
+  for (; issued < min(kAttnStages, n_w); ++issued) issue(issued);
+
+
   // ---- query fragments: rows g and g+8 of the padded 16-head tile, all 8 k-steps
   uint32_t qa[8][4];
   {
@@ -176,36 +221,6 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-
-  // ---- block table entries of this warp, 32 at a time, one per lane
-  const int32_t* table = block_tables + seq * max_blocks;
-  int tab_base = 0;
-  int32_t tab = 0;
-  auto load_tab = [&](int base) {
-    tab_base = base;
-    const int i = base + lane;
-    tab = i < n_w ? table[b0 + warp + kMmaAttnWarps * i] : 0;
-  };
-  // Whole warp calls; lane 0 issues block i of this warp into stage i % kAttnStages.
-  auto issue = [&](int i) {
-    if (i >= tab_base + 32) load_tab(i);
-    int64_t phys = __shfl_sync(0xffffffffu, tab, i - tab_base);
-    if (phys < 0 || phys >= num_blocks) phys = 0;  // never read outside the pool
-    if (lane == 0) {
-      const int s = i % kAttnStages;
-      const uint32_t bar = smem_u32(&s_full[warp][s]);
-      const uint32_t dst = ring + (uint32_t)s * kAttnStageBytes;
-      const int row = (int)((phys * hkv + kvh) * HB_BLOCK_SIZE);
-      mbar_expect_tx(bar, kAttnStageBytes);
-      tma_load_2d(dst, &tm_k, 0, row, bar);
-      tma_load_2d(dst + 2048, &tm_k, 64, row, bar);
-      tma_load_2d(dst + 4096, &tm_v, 0, row, bar);
-      tma_load_2d(dst + 6144, &tm_v, 64, row, bar);
-    }
-  };
-  load_tab(0);
-  int issued = 0;
-  for (; issued < min(kAttnStages, n_w); ++issued) issue(issued);
 
   int done = 0;
   bool ok = true;
@@ -433,7 +448,8 @@ int paged_attention_mma_prepare() {
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int window, int* err_flag, const float* rope_inv_freq) {
+                        int64_t num_blocks, int n_splits, int window, int* err_flag, const float* rope_inv_freq,
+                        int fresh) {
   int rc = paged_attention_mma_prepare();
   if (rc) return rc;
   CUtensorMap tm_k, tm_v;
@@ -461,19 +477,19 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<8>, grid, dim3(256), mma_attn_smem(8), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
                              hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache)));
+                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
     return HB_OK;
   }
   if (nw == 2) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
                              hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache)));
+                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
   } else {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<4>, grid, dim3(128), mma_attn_smem(4), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
                              hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache)));
+                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
   }
   return HB_OK;
 }

@@ -538,6 +538,12 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   consume.rowsq_stride = e->rowsq_stride;
   consume.n = (float)e->H;
   consume.eps = eps;
+  // Rows of one step are different sequences (decode: one new token each) or consecutive
+  // positions of one sequence (prefill chunk): at most B tokens at the end of any context are
+  // written by this step, everything older in the pool is final (HB_ATTN_EARLY=0: the
+  // attention kernel fetches nothing before the q|k|v projection has completed).
+  const char* ae_env = getenv("HB_ATTN_EARLY");
+  const int attn_fresh = (ae_env && ae_env[0] == '0') ? -1 : B;
   const bool rope_epi = e->use_tc && sp->rope_epi;
   if (rope_epi) {
     // the step's (cos, sin) table, shared by the q|k|v epilogues of every layer
@@ -575,7 +581,8 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype, e->d_err, (int)e->window, e->fuse_rope ? e->d_inv_freq : nullptr))) return rc;
+                              e->dtype, e->d_err, (int)e->window, e->fuse_rope ? e->d_inv_freq : nullptr,
+                              attn_fresh))) return rc;
     e->last_launches += 1 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);
