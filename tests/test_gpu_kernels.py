@@ -207,7 +207,9 @@ def test_paged_attention_ignores_garbage_past_context(hb, cuda):
 
 # -------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("M,N,K_", [(1, 256, 256), (8, 1024, 512), (64, 4096, 4096), (64, 6144, 4096), (33, 1000, 320),
-                                    (128, 8192, 1024), (256, 512, 3584), (1, 128, 64), (17, 8, 64), (300, 256, 128)])
+                                    (128, 8192, 1024), (256, 512, 3584), (1, 128, 64), (17, 8, 64), (300, 256, 128),
+                                    # one rank's projections of the 70B shape at TP=4
+                                    (128, 2560, 8192), (128, 8192, 2048), (128, 8192, 7168)])
 def test_gemm_bf16_tensor_core(hb, cuda, M, N, K_):
     """bf16, K % 64 == 0: the tcgen05 path.  fp32 reference of the same op in torch."""
     g = torch.Generator(device="cpu").manual_seed(M * 7 + N)
@@ -268,7 +270,8 @@ def test_argmax_first_maximum(hb, cuda):
     assert got.tolist() == np.argmax(x, axis=1).tolist()
 
 
-@pytest.mark.parametrize("M,I,K_", [(16, 1024, 512), (64, 14336, 4096), (128, 3584, 8192), (5, 688, 256)])
+@pytest.mark.parametrize("M,I,K_", [(16, 1024, 512), (64, 14336, 4096), (128, 3584, 8192), (128, 7168, 8192),
+                                    (5, 688, 256)])
 @pytest.mark.parametrize("splits", [0, 1, 3])
 def test_gemm_swiglu_epilogue(hb, cuda, M, I, K_, splits):
     """gate, up, SiLU and the product in the GEMM epilogue == the unfused sequence
