@@ -189,3 +189,20 @@ def test_no_fallback_without_gpu(hb):
     with pytest.raises(hb.HbError):
         hb.Engine.create_random(dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1,
                                      num_attention_heads=2, vocab_size=64))
+
+
+def test_missing_library_fails_the_import(tmp_path):
+    """There is no fallback path: without the built library (here: HB_LIBRARY pointing at a
+    file that does not exist) importing the package raises instead of degrading."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    code = ("import sys; sys.path.insert(0, %r); import __graft_entry__ as e\n"
+            "try:\n    e.load_package()\nexcept ImportError as ex:\n    print('IMPORT-ERROR', ex); sys.exit(7)\n"
+            "sys.exit(0)\n") % str(root)
+    env = dict(**__import__("os").environ, HB_LIBRARY=str(tmp_path / "libhb_absent.so"))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert res.returncode == 7, res.stdout + res.stderr
+    assert "IMPORT-ERROR" in res.stdout and "libhb_absent.so" in res.stdout
