@@ -9,15 +9,17 @@
 // mma.sync.m16n8k16 (the query heads padded to the 16 MMA rows), which cuts the issue
 // count per KV block about sevenfold, and the KV blocks arrive by TMA:
 //
-//   CTA = (sequence, kv head, KV split), four warps.  Warp w owns the blocks
-//   b0+w, b0+w+4, ... of the CTA's range and keeps its own online-softmax state, so
+//   CTA = (sequence, kv head, KV split), NW = 2, 4 or 8 warps.  Warp w owns the blocks
+//   b0+w, b0+w+NW, ... of the CTA's range and keeps its own online-softmax state, so
 //   the main loop has no CTA-wide barrier.  Each warp has a ring of kAttnStages
 //   stages; one stage holds a block's K and V ([16 tokens][128] bf16 each) as four
 //   [16 x 64] boxes with the 128-byte swizzle, so that ldmatrix reads them without
 //   bank conflicts.  Lane 0 issues the four TMA loads of a block on the stage's
 //   mbarrier; the warp waits for it, computes S = Q K^T (16 MMAs), the online softmax
 //   in fp32, O += P V (16 MMAs, P rounded to bf16), and refills the stage.
-//   At the end the four warps merge their (m, l, O) through shared memory.
+//   At the end the warps merge their (m, l, O) through shared memory.
+//   When the caller bounds the tokens that the preceding kernels write (the engine's
+//   step), the ring is filled with older blocks before griddepcontrol.wait.
 //
 // Every wait is bounded: on expiry the CTA raises *err_flag (when given), writes NaN
 // to its outputs, lets outstanding copies land and returns.

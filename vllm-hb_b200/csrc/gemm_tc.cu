@@ -9,9 +9,17 @@
 // boxes with the 128-byte swizzle straight into shared memory and tcgen05.mma reads
 // them through shared-memory descriptors; the fp32 accumulator [128 x m_pad] lives in
 // tensor memory.  Split-K spreads a weight matrix with few row slabs over all SMs:
-// every CTA owns (slab, K range), writes its fp32 partial to scratch, and the last
-// CTA to arrive for a slab sums the partials in split order (deterministic) and runs
-// the epilogue.
+// every CTA owns (slab, K range).  The partners of a slab form a thread-block cluster:
+// CTA r owns the batch rows [r*m_pad/S, (r+1)*m_pad/S) of the tile, receives the other
+// partners' accumulator columns for those rows through distributed shared memory, adds
+// them in split order (deterministic) and runs the epilogue; the output tile leaves
+// through one bulk tensor store.  Plans that cannot form a cluster write fp32 partials
+// to global scratch and the last CTA to arrive for a slab sums them.
+// Epilogues: store (bf16 / fp32), SwiGLU over [gate ; up] slabs, residual add with the
+// deferred RMSNorm (producer and consumer side, TcNormLink), RoPE + paged KV write for
+// the q|k|v projection, per-expert routing weight.
+// The kernel is launched programmatically: it requests its first weight stages before
+// griddepcontrol.wait (weights never depend on the previous kernel), activations after.
 //
 // CTA = 4 warps.  Warp 0 lane 0 issues TMA, warp 1 lane 0 issues MMAs, all four warps
 // read the accumulator (warp w owns TMEM lanes 32w..32w+31 = output features).
