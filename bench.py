@@ -21,6 +21,12 @@ import threading
 import time
 from pathlib import Path
 
+# The CPU arm uses every host core through the BLAS behind NumPy.  torch.distributed.run
+# exports OMP_NUM_THREADS=1 to its workers; that must be undone BEFORE NumPy loads its BLAS.
+if "--impl" in sys.argv and "reference" in sys.argv:
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
+
 import numpy as np
 
 ROOT = Path(__file__).resolve().parent
@@ -61,6 +67,43 @@ def workload_for(n_gpus: int, args) -> dict:
     if args.prompt_len:
         w["prompt_len"] = args.prompt_len
     return w
+
+
+def blas_threads() -> int:
+    """Threads the BLAS behind NumPy really uses (not the core count of the box)."""
+    try:
+        from threadpoolctl import threadpool_info
+
+        n = [int(i.get("num_threads", 0)) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if n:
+            return max(n)
+    except Exception:
+        pass
+    try:
+        return int(os.environ.get("OMP_NUM_THREADS", "") or (os.cpu_count() or 1))
+    except ValueError:
+        return os.cpu_count() or 1
+
+
+def cpu_config1() -> dict:
+    """The reference's own CPU-runnable configuration timed on the port, whole: tiny fp32
+    Llama (2 layers, hidden 256, 4/2 heads, FFN 688, vocabulary 32000), 8 prompts of 32
+    uniform token ids (seed 0), 32 greedy tokens each = 1 prefill + 31 decode forwards per
+    sequence, one sequence at a time (src/worker/mod.rs:280-293,349-358,404-409)."""
+    from oracle import llama_ref as R
+
+    cfg = R.TINY_CONFIG
+    oracle = R.LlamaTpOracle(cfg, R.random_weights(cfg, seed=1, std=0.02, norm_ones=True), world_size=1, dtype="f32")
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(8, 32))
+    oracle.greedy_generate(prompts[0].tolist(), 2)  # warm-up
+    t0 = time.perf_counter()
+    n = 0
+    for p in prompts:
+        toks, _ = oracle.greedy_generate(p.tolist(), 32)
+        n += len(toks)
+    dt = time.perf_counter() - t0
+    return {"workload": "tiny fp32 llama, 8 prompts x 32 ids, 32 greedy tokens each, per sequence", "tokens": n,
+            "seconds": dt, "tok_s": n / dt, "threads": blas_threads()}
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -190,8 +233,8 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     w = workload_for(args.gpus, args)
-    threads = os.cpu_count() or 1
     ref = CpuReference(w["shape"], w["prompt_len"])
+    threads = blas_threads()
     vals = []
     for _ in range(args.warmup):
         ref.sample(1, threads)
@@ -205,15 +248,155 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     wall = time.perf_counter() - t0
     v = statistics.median(x["value"] for x in vals)
     base = dict(vals[-1]); base["value"] = v
+    base["config1"] = cpu_config1()
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": w["name"], "batch": w["batch"],
-                                            "prompt_len": w["prompt_len"], "parallelism": "cpu"},
+            "data": "synthetic", "config": gpu_config(w, args.gpus, args.steps),
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def gpu_config(w: dict, world: int, steps: int) -> dict:
+    """The `config` object of both arms: the workload, not how an arm runs it."""
+    return {"workload": w["name"], "batch": w["batch"], "prompt_len": w["prompt_len"], "decode_steps": steps,
+            "layers": w["shape"]["num_hidden_layers"], "parallelism": f"tp{world}",
+            "l2": "inputs larger than L2 (weights + KV read once per step)",
+            "timing": "value: CUDA events around each step's kernels on the engine stream, summed; "
+                      "e2e: wall clock around the K hb_decode_batch calls; max over ranks"}
+
+
+# ------------------------------------------------------------ parity at N > 1 (untimed)
+def tp_parity(hb, tp_world, rank: int, world: int, dev) -> dict:
+    """Checks made on all N ranks before anything is timed, with the CPU oracle as the
+    checker: (1) a small bf16 tensor-parallel model (2 layers, hidden 2048, 16/8 heads of
+    128), 48 sequences, 6 lock-step steps: every rank's logits against LlamaTpOracle with
+    world_size N and against rank 0 bit for bit; (2) hb_all_reduce_add_rms_norm one-shot and
+    two-shot against the rank-order fp32 sum + residual + RMSNorm of the oracle; (3) the
+    row-parallel projection whose GEMM epilogue pushes the first hop, against the same."""
+    import torch
+    import torch.distributed as dist
+    from oracle import kernels_ref as K
+    from oracle import llama_ref as R
+    from oracle import parallel_ref as P
+
+    out = {}
+    shape = dict(hidden_size=2048, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=16,
+                 num_key_value_heads=8, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+    B, steps, n_check = 48, 6, 8
+    eng = hb.Engine.create_random(shape, seed=11, std=0.02, norm_ones=True, max_seq_len=32, bf16=True,
+                                  tensor_parallel_size=world, world=tp_world, max_batch=B)
+    cfg = R.LlamaTpConfig(**shape)
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, steps)).astype(np.uint32)
+    seqs = [eng.create_kv_cache() for _ in range(B)]
+    logits = np.empty((B, cfg.vocab_size), dtype=np.float32)
+    for t in range(steps):
+        eng.decode_batch(seqs, prompts[:, t], logits=logits)
+    local = {name: eng.get_tensor(name) for name in R.tensor_shapes(cfg)}
+    all_w = [None] * world
+    all_l = [None] * world
+    dist.gather_object(local, all_w if rank == 0 else None, dst=0)
+    dist.gather_object(logits, all_l if rank == 0 else None, dst=0)
+    if rank == 0:
+        weights = {}
+        for name, shp in R.tensor_shapes(cfg).items():
+            pieces = [all_w[r][name] for r in range(world)]
+            if name.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "gate_proj.weight", "up_proj.weight")):
+                weights[name] = np.concatenate([p.reshape(shp[0] // world, shp[1]) for p in pieces], 0)
+            elif name.endswith(("o_proj.weight", "down_proj.weight")):
+                weights[name] = np.concatenate([p.reshape(shp[0], shp[1] // world) for p in pieces], 1)
+            else:
+                weights[name] = pieces[0].reshape(shp)
+        oracle = R.LlamaTpOracle(cfg, weights, world_size=world, dtype="bf16", reference_reduce=False, weights_exact=True)
+        rows = np.linspace(0, B - 1, n_check).astype(int)
+        want = np.stack([oracle.forward(prompts[i].tolist(), 0, oracle.new_cache()) for i in rows])
+        scale = float(np.max(np.abs(want)))
+        out["max_rel_err"] = max(float(np.max(np.abs(all_l[r][rows] - want))) / scale for r in range(world))
+        out["ranks_identical"] = all(np.array_equal(all_l[r], all_l[0]) for r in range(world))
+        out["greedy_agreement"] = float(np.mean(np.argmax(all_l[0][rows], 1) == np.argmax(want, 1)))
+        out["model"] = "2 layers, hidden 2048, 16/8 heads, FFN 2048, vocab 4096, bf16, B=48, 6 steps"
+    for s_ in seqs:
+        s_.free()
+    eng.close()
+
+    # (2) exchange + residual + norm kernel, both algorithms, M=64 x N=8192 bf16
+    M, N = 64, 8192
+    parts = [K.round_bf16(np.random.default_rng(10 + r).standard_normal((M, N)).astype(np.float32)) for r in range(world)]
+    resid = K.round_bf16(np.random.default_rng(4).standard_normal((M, N)).astype(np.float32))
+    nw = K.round_bf16((1.0 + 0.1 * np.random.default_rng(5).standard_normal(N)).astype(np.float32))
+    acc = np.zeros((M, N), dtype=np.float32)
+    for p_ in parts:
+        acc = acc + p_                                   # rank order, fp32 (src/parallel/comm.rs:54-58)
+    want_h = K.round_bf16(resid + K.round_bf16(acc))
+    want_n = K.rms_norm_kernel(want_h, nw, 1e-5, "bf16")
+    put = lambda a: torch.from_numpy(a).to(dev, torch.bfloat16)
+    exact, nerr = True, 0.0
+    for algo in (hb.ALGO_ONE_SHOT, hb.ALGO_TWO_SHOT):
+        for _ in range(2):                               # the second call reuses the staging area
+            normed, res = tp_world.all_reduce_add_rms_norm(put(parts[rank]), put(resid), put(nw), 1e-5, algo)
+            torch.cuda.synchronize()
+            exact = exact and bool(np.array_equal(res.float().cpu().numpy(), want_h))
+            nerr = max(nerr, float(np.max(np.abs(normed.float().cpu().numpy() - want_n))) / float(np.max(np.abs(want_n))))
+    # (3) GEMM with the push epilogue + the same kernel starting at its wait
+    Kl = 1024
+    xs = [K.round_bf16(np.random.default_rng(20 + r).standard_normal((M, Kl)).astype(np.float32)) for r in range(world)]
+    wts = [K.round_bf16((0.02 * np.random.default_rng(30 + r).standard_normal((N, Kl))).astype(np.float32)) for r in range(world)]
+    form = hb.fused_rowparallel_form(tp_world, M, N, Kl, hb.ALGO_TWO_SHOT)
+    normed, res = hb.fused_rowparallel(tp_world, put(xs[rank]), put(wts[rank]), put(resid), put(nw), 1e-5, hb.ALGO_TWO_SHOT)
+    torch.cuda.synchronize()
+    acc = resid.copy()
+    for r in range(world):
+        acc = acc + K.round_bf16((xs[r].astype(np.float64) @ wts[r].astype(np.float64).T).astype(np.float32))
+    want_h2 = K.round_bf16(acc)
+    perr = float(np.max(np.abs(res.float().cpu().numpy() - want_h2))) / float(np.max(np.abs(want_h2)))
+    digest = int(np.frombuffer(res.view(torch.int16).cpu().numpy().tobytes(), dtype=np.uint32).sum(dtype=np.uint64))
+    stats = torch.tensor([0.0 if exact else 1.0, nerr, perr, float(tp_world.status() != 0)], dtype=torch.float64, device=dev)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    digests = [None] * world
+    dist.all_gather_object(digests, digest)
+    out.update({"ar_resid_bit_exact": bool(stats[0] == 0.0), "ar_norm_max_rel_err": float(stats[1]),
+                "push_form": form, "push_max_rel_err": float(stats[2]), "push_ranks_identical": len(set(digests)) == 1,
+                "world_status_clean": bool(stats[3] == 0.0)})
+    ok = (out.get("max_rel_err", 0.0) <= 2e-2 and out.get("ranks_identical", True) and out["ar_resid_bit_exact"]
+          and out["ar_norm_max_rel_err"] <= 2e-2 and out["push_max_rel_err"] <= 2e-2 and out["push_ranks_identical"]
+          and out["world_status_clean"])
+    out["ok"] = bool(ok)
+    return out
+
+
+def tp1_same_shape(hb, shape: dict, B: int, P: int, layers: int, steps: int) -> dict:
+    """The N > 1 workload's shape on ONE GPU with `layers` layers (the full depth does not fit
+    180 GB): per-layer time from the per-kind profile, scaled to the full depth plus the
+    lm_head and the small kernels, so that the TP=1/2/4/8 curve has its base on one workload."""
+    full = shape["num_hidden_layers"]
+    sh = dict(shape, num_hidden_layers=layers)
+    eng = hb.Engine.create_random(sh, seed=1, std=0.02, norm_ones=True, max_seq_len=P + steps + 16, bf16=True,
+                                  tensor_parallel_size=1, world=None, max_batch=B)
+    prompts = np.random.default_rng(0).integers(0, sh["vocab_size"], size=(B, P)).astype(np.uint32)
+    seqs = [eng.create_kv_cache() for _ in range(B)]
+    nxt = np.empty(B, dtype=np.uint32)
+    for t in range(P):
+        eng.decode_batch(seqs, prompts[:, t], next_tokens=nxt)
+    for _ in range(3):
+        eng.decode_batch(seqs, nxt.copy(), next_tokens=nxt)
+    ms = 0.0
+    for _ in range(steps):
+        eng.decode_batch(seqs, nxt.copy(), next_tokens=nxt)
+        ms += eng.last_step_ms()
+    ms /= steps
+    _, prof = eng.profile_step(seqs, nxt.copy())
+    fixed = prof.get("gemm_lm_head", 0.0) + prof.get("other", 0.0)
+    fixed = min(fixed, 0.5 * ms)
+    full_ms = (ms - fixed) * full / layers + fixed
+    for s_ in seqs:
+        s_.free()
+    eng.close()
+    return {"layers_run": layers, "ms_per_step_run": ms, "ms_per_step_full_depth": full_ms,
+            "value": B / (full_ms / 1e3), "unit": UNIT,
+            "how": f"{layers} of {full} layers on one GPU, B={B}, prompt {P}; (step - lm_head - small kernels) "
+                   f"x {full}/{layers} + lm_head + small kernels"}
 
 
 # ------------------------------------------------------------------------- GPU arm
@@ -233,9 +416,17 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     max_seq = P + W + K + args.profile_steps + 8
 
     tp_world = None
+    parity = same_shape = None
+    dev = torch.device("cuda", local_rank)
     if world > 1:
         staging = 64 << 20
-        tp_world = hb.TpWorld.from_torch_distributed(local_rank, staging_bytes=staging, nccl=False)
+        tp_world = hb.TpWorld.from_torch_distributed(local_rank, staging_bytes=staging, nccl=True)
+        if args.workload == "auto" and not args.skip_checks:
+            # correctness on all N ranks first (untimed); a failure ends the run non-zero
+            parity = tp_parity(hb, tp_world, rank, world, dev)
+            if rank == 0:
+                same_shape = tp1_same_shape(hb, shape, B, P, args.tp1_layers, 8)
+            dist.barrier()
     eng = hb.Engine.create_random(shape, seed=1, std=0.02, norm_ones=w["norm_ones"], max_seq_len=max_seq,
                                   bf16=True, tensor_parallel_size=world, world=tp_world, max_batch=B)
     prompts = np.random.default_rng(0).integers(0, shape["vocab_size"], size=(B, P)).astype(np.uint32)
@@ -287,6 +478,13 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         dist.all_gather_object(gathered, {k: round(v, 4) for k, v in prof.items()})
         prof_ranks = {k: [g.get(k, 0.0) for g in gathered] for k in ("all_reduce", "gemm", "attention")}
 
+    rowpar = None
+    if world > 1 and args.workload == "auto" and not args.skip_checks:
+        import vllm_hb_b200.bench_rowparallel as brp
+
+        peak0, _ = measured_peaks()
+        rowpar = brp.run_points(hb, tp_world, rank, world, dev, peak0)
+
     ctx_mid = [P + W + K // 2 + 1] * B
     step_bytes = eng.step_bytes(ctx_mid)
     gemm_bytes = eng.gemm_bytes(B)
@@ -317,16 +515,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["name"], "batch": B, "prompt_len": P, "decode_steps": K,
-                       "layers": shape["num_hidden_layers"], "parallelism": f"tp{world}",
-                       "l2": "inputs larger than L2 (weights + KV read once per step)",
-                       "timing": "value: CUDA events around each step's kernels on the engine stream, summed; "
-                                 "e2e: wall clock around the K hb_decode_batch calls; max over ranks"},
+            "config": gpu_config(w, world, K),
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B + 4},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (all GEMM launches of a step)",
                          "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                          "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                         "traffic_source": "DRAM read+write bytes of the ncu captures summarised in "
+                                           "profiles/gemm_tc_kernel_decode_shapes.md (not measured by this run)",
                          "algorithmic_bytes_per_step": gemm_bytes, "ms_per_step": gemm_ms,
                          "timing": "CUDA events recorded between the kernels of profile steps on the engine stream (graph with event nodes)"},
             "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (dev_ms / K / 1e3) / 1e9,
@@ -336,8 +532,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline and args.workload == "auto":
-            threads = os.cpu_count() or 1
-            line["cpu_baseline"] = cpu_reference_tok_s(shape, P, 4, threads)
+            line["cpu_baseline"] = cpu_reference_tok_s(shape, P, 4, blas_threads())
+            line["cpu_baseline"]["config1"] = cpu_config1()
+        if parity is not None:
+            line["tp_parity"] = parity
+        if same_shape is not None:
+            line["tp1_same_shape"] = same_shape
+        if rowpar is not None:
+            line["rowparallel"] = rowpar
         print(json.dumps(line), flush=True)
     for s in seqs:
         s.free()
@@ -347,6 +549,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         tp_world.close()
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity.get("ok", True):
+        raise SystemExit("tensor-parallel parity check failed: " + json.dumps(parity))
 
 
 def main() -> None:
@@ -361,6 +565,9 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--profile-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-checks", action="store_true",
+                    help="N > 1: skip the untimed parity checks, the single-GPU base point and the row-parallel points")
+    ap.add_argument("--tp1-layers", type=int, default=8, help="layers of the single-GPU base point of the N > 1 shape")
     ap.add_argument("--workload", default="auto", choices=["auto", "mixtral"],
                     help="auto: Llama-3.1-8B shape on one GPU, 70B shape on several; mixtral: Mixtral-8x7B shape")
     args = ap.parse_args()

@@ -47,7 +47,7 @@ typedef enum hb_dtype { HB_F32 = 0, HB_F16 = 1, HB_BF16 = 2 } hb_dtype;
 typedef enum hb_algo {
   HB_ALGO_AUTO = 0,     /* one-shot below the crossover size, two-shot above */
   HB_ALGO_ONE_SHOT = 1, /* every rank reads all partials: (R-1)*bytes inbound, one flag hop */
-  HB_ALGO_TWO_SHOT = 2, /* reduce-scatter by column slice + all-gather: 2(R-1)/R*bytes */
+  HB_ALGO_TWO_SHOT = 2, /* reduce-scatter + all-gather: 2(R-1)/R*bytes, two flag hops */
   HB_ALGO_NCCL = 3      /* ncclAllReduce: the reference's path, kept as the reported baseline */
 } hb_algo;
 
@@ -115,7 +115,8 @@ int hb_kv_assign_paged(void* stream, void* k_cache, void* v_cache, const void* k
 /* Paged GQA decode attention: one query token per sequence over that sequence's
  * block table.  q,out [n_seqs, n_q_heads, head_dim]; block_tables int32
  * [n_seqs, max_blocks_per_seq]; ctx_lens int32 [n_seqs] (number of keys, including
- * the token just written).  Query head j reads kv head j / (n_q_heads/n_kv_heads)
+ * the token just written; an entry above max_blocks_per_seq*16 is cut to that, block ids
+ * outside [0, num_blocks) read block 0: nothing outside the tables and the pool is touched).  Query head j reads kv head j / (n_q_heads/n_kv_heads)
  * (src/engine/arch/llama_tp.rs:264-279); scores = q.k/sqrt(d), softmax and the
  * weighted sum accumulate in fp32 (src/engine/arch/llama_tp.rs:304-324).
  * `workspace` holds split-KV partials: hb_attention_workspace_bytes() bytes.
@@ -217,7 +218,10 @@ typedef struct hb_world hb_world;
 
 /* Single-process form of TpWorld::new(n) (src/parallel/world.rs:95-133): worlds_out
  * receives n handles, rank i on device_ids[i] (NULL = 0..n-1).  Fails with a message
- * naming tensor_parallel_size when fewer devices are visible. */
+ * naming tensor_parallel_size when fewer devices are visible.  An explicit device_ids
+ * list may name one device several times (ranks sharing a GPU; their kernels wait for
+ * one another, so launch them only where they are known to run concurrently, or use
+ * it to exercise the timeout path with hb_world_set_wait_limit). */
 int hb_world_create_local(int n, const int* device_ids, size_t staging_bytes,
                           hb_world** worlds_out);
 /* One-process-per-GPU form: create this rank's side, export its handle ... */
@@ -242,9 +246,22 @@ int hb_world_device(const hb_world* w); /* TpWorld::device, world.rs:145 */
 int hb_world_is_single(const hb_world* w); /* TpWorld::is_single, world.rs:157 */
 size_t hb_world_staging_bytes(const hb_world* w);
 void* hb_world_stream(const hb_world* w);
-/* Device status word of the last collective on this rank: 0, or HB_ERR_TIMEOUT when a
- * bounded wait on a peer flag ran out (the kernel then returns instead of hanging). */
+/* Device status word of the collectives on this rank since the last call: 0, or
+ * HB_ERR_TIMEOUT when a bounded wait on a peer flag ran out (the kernel then returns
+ * instead of hanging, as nccl_all_reduce returns an Err: src/parallel/comm.rs:113-143).
+ * Reading a non-zero status clears it.  After a timeout the outputs of that collective
+ * are undefined and the sequence counters of the ranks may disagree: free the worlds of
+ * the group and create new ones before the next collective. */
 int hb_world_status(hb_world* w);
+/* Number of polls after which a device-side wait on a peer flag gives up (0 restores
+ * the default of 2^22, several hundred milliseconds).  Applies to collectives launched
+ * afterwards; a step already captured in a CUDA graph keeps the limit it was captured
+ * with.  (No counterpart in the reference: NCCL's own watchdog plays this part there.) */
+int hb_world_set_wait_limit(hb_world* w, uint32_t polls);
+/* on != 0: the exchange kernels signal early that the next kernel of the stream may become
+ * resident (programmatic dependent launch), so that a GEMM launched after them requests
+ * its weights while the exchange waits for its peers.  Off by default. */
+int hb_world_set_early_trigger(hb_world* w, int on);
 
 /* In-place SUM all-reduce of `count` elements at `buf` on this rank; every rank calls
  * it with the same count/dtype.  The result is valid on every rank (a superset of the
@@ -268,13 +285,30 @@ int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void
                                int64_t rows, int64_t hidden, float eps, hb_dtype dtype, hb_algo algo);
 
 /* Fused row-parallel projection: normed_out = rms_norm(resid_out),
- * resid_out = resid_in + SUM_ranks( X_r[M,Kl] . W_r[N,Kl]^T ), one kernel per rank:
- * tcgen05 GEMM tiles are pushed to the owning peer's staging over NVLink, reduced
- * there with the residual, gathered back with the row statistics, and normalised.
+ * resid_out = resid_in + SUM_ranks( X_r[M,Kl] . W_r[N,Kl]^T ).
  * This is llama_tp.rs steps o_proj/down_proj -> all_reduce -> residual -> next norm
- * (src/engine/arch/llama_tp.rs:327,533-552 and :339,563-571,517-522).
- * bf16 only.  With a single-rank world it is the same kernel without the exchange.
+ * (src/engine/arch/llama_tp.rs:327,533-552 and :339,563-571,517-522).  bf16 only.
+ * The form depends on the world, the shape and `algo` (hb_fused_rowparallel_form tells
+ * which; nothing is substituted silently):
+ *   HB_ROWPAR_SINGLE    single-rank world: tcgen05 GEMM, then add + RMSNorm;
+ *   HB_ROWPAR_PUSH      the GEMM epilogue writes each 128-feature tile of the partial
+ *                       straight into the staging of the rank that reduces that column
+ *                       slice (NVLink peer stores + a release flag per tile): the first hop
+ *                       of the all-reduce is part of the GEMM kernel; one peer-memory kernel
+ *                       then sums, adds the residual, returns the reduced slices and
+ *                       normalises.  Taken with HB_ALGO_TWO_SHOT, or HB_ALGO_AUTO above
+ *                       128 KiB on 3+ ranks, when N is a multiple of 128*ranks, M <= 256;
+ *   HB_ROWPAR_EXCHANGE  GEMM to a local partial, then hb_all_reduce_add_rms_norm
+ *                       (HB_ALGO_ONE_SHOT, small messages, shapes the push form cannot take);
+ *   HB_ROWPAR_NCCL      GEMM -> ncclAllReduce -> add + RMSNorm, the reference's own sequence
+ *                       (HB_ALGO_NCCL; needs hb_world_init_nccl): the reported baseline.
+ * Shapes none of the forms covers fail with HB_ERR_INVALID_ARG.
  * norm_w may be NULL (then normed_out is not written). */
+#define HB_ROWPAR_SINGLE 0
+#define HB_ROWPAR_PUSH 1
+#define HB_ROWPAR_EXCHANGE 2
+#define HB_ROWPAR_NCCL 3
+int hb_fused_rowparallel_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_algo algo);
 size_t hb_fused_rowparallel_workspace_bytes(int64_t M, int64_t N, int64_t K_local);
 int hb_fused_rowparallel(hb_world* w, void* stream, void* normed_out, void* resid_out,
                          const void* X, const void* W, const void* resid_in, const void* norm_w,

@@ -13,6 +13,13 @@ source is not in the tree; same architecture: rotate-half RoPE, pre-norm, SwiGLU
 
 dtype "f32" does no intermediate rounding; "bf16"/"f16" round wherever the reference
 materialises a tensor (after each matmul, RoPE, softmax in dtype per llama_tp.rs:318).
+``eager`` selects which of the reference's two arithmetic forms the norm and RoPE take in
+a 16-bit dtype:
+  eager=True  (default for "bf16")  the multi-op path the reference runs for bf16: RMSNorm as
+              candle_fallback, every op rounded (src/kernels/rms_norm.rs:128-132), RoPE with
+              every product and sum rounded (llama_tp.rs:135-149);
+  eager=False (default for "f32"/"f16") the fused-kernel numerics: fp32 accumulation, one
+              rounding (kernels/rms_norm.cu:74-110, kernels/rope.cu:36-39).
 """
 from __future__ import annotations
 
@@ -54,7 +61,8 @@ class LlamaTpConfig:
 
 class LlamaTpOracle:
     def __init__(self, cfg: LlamaTpConfig, weights: dict, world_size: int = 1, dtype: str = "f32",
-                 reference_reduce: bool = True, softmax_in_dtype: bool = True):
+                 reference_reduce: bool = True, softmax_in_dtype: bool = True, eager=None,
+                 weights_exact: bool = False):
         n = world_size
         # divisibility rules of TpLlamaBackend::load (llama_tp.rs:407-427)
         if cfg.num_attention_heads % n:
@@ -69,9 +77,13 @@ class LlamaTpOracle:
         self.cfg, self.n, self.dtype = cfg, n, dtype
         self.reference_reduce = reference_reduce
         self.softmax_in_dtype = softmax_in_dtype
+        self.eager = (dtype == "bf16") if eager is None else bool(eager)
         self.local_heads = cfg.num_attention_heads // n
         self.local_kv_heads = cfg.kv_heads() // n
-        r = lambda a: K.rnd(np.asarray(a, dtype=np.float32), dtype)  # load_all_weights casts to dtype (:367-377)
+        # load_all_weights casts to dtype (:367-377); weights_exact: the caller's values already
+        # are representable in dtype (read back from a device that holds them in it)
+        r = (lambda a: np.asarray(a, dtype=np.float32)) if weights_exact else \
+            (lambda a: K.rnd(np.asarray(a, dtype=np.float32), dtype))
         g = lambda name: r(weights[name])
         self.embed = g("model.embed_tokens.weight")
         self.final_norm = g("model.norm.weight")
@@ -103,6 +115,8 @@ class LlamaTpOracle:
         return K.rnd(x @ w.T, self.dtype)
 
     def _norm(self, x, w):
+        if self.eager:
+            return K.rms_norm_fallback(x, w, self.cfg.rms_norm_eps, self.dtype)
         return K.rms_norm_kernel(x, w, self.cfg.rms_norm_eps, self.dtype)
 
     def attn_partial(self, rank, x, layer, seq_pos, cache):
@@ -114,8 +128,8 @@ class LlamaTpOracle:
         k = self._mm(x, w["k"]).reshape(seq, self.local_kv_heads, d)
         v = self._mm(x, w["v"]).reshape(seq, self.local_kv_heads, d)
         cos, sin = K.rope_tables(np.arange(seq_pos, seq_pos + seq), cfg.rope_theta, d, dt)
-        q = K.apply_rope(q, cos, sin, dt)
-        k = K.apply_rope(k, cos, sin, dt)
+        q = K.apply_rope(q, cos, sin, dt, per_op_rounding=self.eager)
+        k = K.apply_rope(k, cos, sin, dt, per_op_rounding=self.eager)
         kc, vc = cache[rank][layer]
         k = k if kc is None else np.concatenate([kc, k], axis=0)  # Tensor::cat (:245-259)
         v = v if vc is None else np.concatenate([vc, v], axis=0)
@@ -147,8 +161,15 @@ class LlamaTpOracle:
         return (P.all_reduce if self.reference_reduce else P.all_reduce_f32)(partials, self.dtype)
 
     # ----------------------------------------------------------------- forward
-    def forward(self, token_ids, seq_pos: int, cache, return_hidden: bool = False):
-        """TpLlamaBackend::forward (llama_tp.rs:506-576) -> logits [vocab] of the last token."""
+    def final_logits(self, hidden_rows):
+        """final_forward (llama_tp.rs:349-356) for a stack of last-token hidden rows [n, H]."""
+        normed = self._norm(np.asarray(hidden_rows, dtype=np.float32), self.final_norm)
+        return K.rnd(normed @ self.lm_head.T, self.dtype)
+
+    def forward(self, token_ids, seq_pos: int, cache, return_hidden: bool = False, logits: bool = True):
+        """TpLlamaBackend::forward (llama_tp.rs:506-576) -> logits [vocab] of the last token.
+        logits=False returns the hidden rows only (final_logits() then serves many
+        sequences with one lm_head product)."""
         cfg, dt = self.cfg, self.dtype
         ids = np.asarray(token_ids, dtype=np.int64)
         hidden = self.embed[ids]  # identical on every rank (:508-512)
@@ -160,6 +181,8 @@ class LlamaTpOracle:
             post = self._norm(after_attn, self.ranks[0][layer]["post_norm"])
             ffn = self._reduce([self.ffn_partial(r, post, layer) for r in range(self.n)])
             hidden = K.rnd(after_attn + ffn, dt)
+        if not logits:
+            return hidden
         normed = self._norm(hidden, self.final_norm)
         logits = K.rnd(normed[-1:] @ self.lm_head.T, dt)[0]  # final_forward (:349-356)
         return (logits, hidden) if return_hidden else logits

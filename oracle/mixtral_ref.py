@@ -89,6 +89,7 @@ class MixtralOracle:
         if cfg.num_attention_heads % n or cfg.kv_heads() % n or cfg.intermediate_size % n:
             raise ValueError("heads, kv heads and intermediate_size must be divisible by tensor_parallel_size")
         self.cfg, self.n, self.dtype = cfg, n, dtype
+        self.min_route_gap = float("inf")  # reset by the caller between sequences
         self.local_heads = cfg.num_attention_heads // n
         self.local_kv_heads = cfg.kv_heads() // n
         r = lambda a: K.rnd(np.asarray(a, dtype=np.float32), dtype)
@@ -159,7 +160,15 @@ class MixtralOracle:
         dt = self.dtype
         logits = self._mm(x, self.ranks[0][layer]["gate"])
         probs = K.rnd(K.softmax_last(logits.astype(np.float64)).astype(np.float32), dt)
-        return [route(probs[t], self.cfg.num_experts_per_tok) for t in range(x.shape[0])]
+        # The reference picks the top-k with an unstable sort (mixtral.rs:395-397): which expert
+        # wins a tie, or a gap smaller than the arithmetic noise, is unspecified.  The smallest
+        # gap between the last chosen and the first rejected probability is recorded so that a
+        # parity test can tell a different-but-legal choice from an error.
+        k = self.cfg.num_experts_per_tok
+        if probs.shape[1] > k:
+            srt = np.sort(probs, axis=1)[:, ::-1]
+            self.min_route_gap = min(self.min_route_gap, float(np.min(srt[:, k - 1] - srt[:, k])))
+        return [route(probs[t], k) for t in range(x.shape[0])]
 
     def moe_partial(self, rank, x, layer, routes):
         """SparseMoeBlock::forward (mixtral.rs:371-430) with this rank's slice of every expert:

@@ -1,6 +1,7 @@
-"""hb_fused_rowparallel on one rank: o_proj/down_proj + residual + RMSNorm in one
-kernel against the unfused oracle sequence (src/engine/arch/llama_tp.rs:327,533-552):
-partial = bf16(x . W^T); h' = bf16(resid + partial); normed = rms_norm(h'; w)."""
+"""hb_fused_rowparallel on one rank (the "single" form: tcgen05 GEMM, then add + RMSNorm)
+against the oracle sequence (src/engine/arch/llama_tp.rs:327,533-552):
+partial = bf16(x . W^T); h' = bf16(resid + partial); normed = rms_norm(h'; w).
+The multi-rank forms are covered on 2+ GPUs and by bench.py at every N > 1."""
 import numpy as np
 import pytest
 import torch
@@ -41,6 +42,7 @@ def make(M, N, Kl, seed, cuda):
                                     (128, 8192, 1024), (128, 8192, 3584), (256, 2048, 640), (17, 384, 128)])
 def test_fused_single_rank(hb, cuda, M, N, Kl):
     x, w, resid, nw = make(M, N, Kl, M + N, cuda)
+    assert hb.fused_rowparallel_form(None, M, N, Kl) == "single"
     normed, res = hb.fused_rowparallel(None, x, w, resid, nw, 1e-5)
     torch.cuda.synchronize()
     want_n, want_h = reference([host(x)], [host(w)], host(resid), host(nw), 1e-5)
@@ -50,8 +52,8 @@ def test_fused_single_rank(hb, cuda, M, N, Kl):
 
 
 def test_fused_equals_unfused_sequence(hb, cuda):
-    """Same inputs through GEMM -> add + RMSNorm (three launches) and through the fused
-    kernel: identical rounding points, so the outputs agree to bf16 resolution."""
+    """Same inputs through hb_gemm -> hb_add_rms_norm called one by one and through the entry
+    point: identical rounding points, so the outputs agree to bf16 resolution."""
     M, N, Kl = 64, 4096, 4096
     x, w, resid, nw = make(M, N, Kl, 3, cuda)
     normed, res = hb.fused_rowparallel(None, x, w, resid, nw, 1e-5)
@@ -62,8 +64,8 @@ def test_fused_equals_unfused_sequence(hb, cuda):
 
 
 def test_fused_reuses_workspace_and_is_deterministic(hb, cuda):
-    """Sequence numbers live in the workspace: back-to-back calls on one workspace give
-    bit-identical results (split-K and the tile protocol have a fixed order)."""
+    """Back-to-back calls on one workspace give bit-identical results (split-K partials are
+    summed in a fixed order)."""
     M, N, Kl = 64, 4096, 14336
     x, w, resid, nw = make(M, N, Kl, 5, cuda)
     ws = hb.fused_rowparallel_workspace(x, w)

@@ -1,8 +1,11 @@
 """Tensor-parallel pieces on 2+ GPUs of one box, driven from one process the way the
 reference drives its ranks (src/engine/arch/llama_tp.rs:506-576): the peer-memory
-all-reduce against the rank-order sum of src/parallel/comm.rs:47-62, and the fused
-row-parallel kernel against the unfused oracle.  Skipped on a single-GPU box."""
+all-reduce against the rank-order sum of src/parallel/comm.rs:47-62, the NCCL baseline,
+the row-parallel projection whose GEMM epilogue pushes the first hop of the exchange, the
+tensor-parallel engines (Llama and Mixtral) against the oracle, and a wait that runs out.
+Skipped on a single-GPU box (bench.py repeats the parity checks at every N > 1)."""
 import os
+import threading
 
 import numpy as np
 import pytest
@@ -153,7 +156,15 @@ def test_fused_rowparallel(hb, worlds, M, N, K_, algo):
 
     ins = on_all(worlds, lambda r, w: (put(xs[r], w), put(wt[r], w), put(resid, w), put(nw, w)))
     wss = on_all(worlds, lambda r, w: hb.fused_rowparallel_workspace(ins[r][0], ins[r][1]))
-    for rep in range(2):
+    # which form runs is part of the contract: two-shot = the GEMM epilogue pushes the first hop
+    form = hb.fused_rowparallel_form(worlds[0], M, N, Kl, code)
+    if algo == "two_shot":
+        assert form == "push"
+    elif algo == "one_shot":
+        assert form == "exchange"
+    else:
+        assert form == ("push" if R > 2 and M * N * 2 > 128 * 1024 else "exchange")
+    for rep in range(3):
         outs = on_all(worlds, lambda r, w: hb.fused_rowparallel(w, *ins[r], 1e-5, code, workspace=wss[r]))
         assert all(w.status() == 0 for w in worlds)
         parts = [K.round_bf16((xs[r].astype(np.float64) @ wt[r].astype(np.float64).T).astype(np.float32)) for r in range(R)]
@@ -171,20 +182,25 @@ def test_fused_rowparallel(hb, worlds, M, N, K_, algo):
             assert np.array_equal(host(res), host(outs[0][1])) and np.array_equal(host(normed), host(outs[0][0]))
 
 
-@pytest.mark.parametrize("fused", ["0", "1"])
-def test_tp_engine_matches_oracle(hb, worlds, fused, monkeypatch):
-    """A small bf16 model sharded over the ranks: logits of every rank against the
-    oracle with the same world size, with the row-parallel projections as separate
-    kernels (fused=0) and as the one-kernel fused form (fused=1)."""
-    monkeypatch.setenv("HB_FUSED", fused)
-    from oracle import llama_ref as R_
+def run_lockstep(engines, seqs, tokens, logits):
+    """One decode step on every rank: a rank's step blocks until its peers arrive, so
+    every rank gets a host thread."""
+    errs = []
 
-    R = len(worlds)
-    shape = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=16,
-                 num_key_value_heads=8, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
-    engines = on_all(worlds, lambda r, w: hb.Engine.create_random(shape, seed=1, norm_ones=True, max_seq_len=64,
-                                                                   bf16=True, tensor_parallel_size=R, world=w, max_batch=8))
-    cfg = R_.LlamaTpConfig(**shape)
+    def one(r):
+        try:
+            engines[r].decode_batch(seqs[r], tokens, logits=logits[r])
+        except Exception as e:  # surfaced below: a dead thread must not hang the others silently
+            errs.append((r, e))
+
+    ths = [threading.Thread(target=one, args=(r,)) for r in range(len(engines))]
+    [th.start() for th in ths]
+    [th.join() for th in ths]
+    assert not errs, errs
+
+
+def gather_llama_weights(engines, cfg, R_):
+    R = len(engines)
     weights = {}
     for name, shp in R_.tensor_shapes(cfg).items():
         pieces = [engines[r].get_tensor(name) for r in range(R)]
@@ -194,19 +210,31 @@ def test_tp_engine_matches_oracle(hb, worlds, fused, monkeypatch):
             weights[name] = np.concatenate([p.reshape(shp[0], shp[1] // R) for p in pieces], 1)
         else:
             weights[name] = pieces[0].reshape(shp)
-    oracle = R_.LlamaTpOracle(cfg, weights, world_size=R, dtype="bf16", reference_reduce=False)
+    return weights
+
+
+@pytest.mark.parametrize("push", ["0", "1"])
+def test_tp_engine_matches_oracle(hb, worlds, push, monkeypatch):
+    """A small bf16 model sharded over the ranks: logits of every rank against the
+    oracle with the same world size, with the row-parallel projections as GEMM + exchange
+    kernel (push=0) and with the first hop pushed by the GEMM epilogue (push=1)."""
+    monkeypatch.setenv("HB_PUSH", push)
+    from oracle import llama_ref as R_
+
+    R = len(worlds)
+    shape = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=16,
+                 num_key_value_heads=8, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+    engines = on_all(worlds, lambda r, w: hb.Engine.create_random(shape, seed=1, norm_ones=True, max_seq_len=64,
+                                                                   bf16=True, tensor_parallel_size=R, world=w, max_batch=8))
+    cfg = R_.LlamaTpConfig(**shape)
+    weights = gather_llama_weights(engines, cfg, R_)
+    oracle = R_.LlamaTpOracle(cfg, weights, world_size=R, dtype="bf16", reference_reduce=False, weights_exact=True)
     B, plen = 8, 6
     prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, plen)).astype(np.uint32)
     seqs = on_all(worlds, lambda r, w: [engines[r].create_kv_cache() for _ in range(B)])
     logits = [np.empty((B, cfg.vocab_size), dtype=np.float32) for _ in range(R)]
-    import threading
-
     for t in range(plen):
-        # every rank's step blocks until its peers arrive: one host thread per rank
-        ths = [threading.Thread(target=lambda r=r: engines[r].decode_batch(seqs[r], prompts[:, t], logits=logits[r]))
-               for r in range(R)]
-        [th.start() for th in ths]
-        [th.join() for th in ths]
+        run_lockstep(engines, seqs, prompts[:, t], logits)
     want = np.stack([oracle.forward(prompts[i].tolist(), 0, oracle.new_cache()) for i in range(B)])
     for r in range(R):
         err = float(np.max(np.abs(logits[r] - want))) / float(np.max(np.abs(want)))
@@ -214,3 +242,153 @@ def test_tp_engine_matches_oracle(hb, worlds, fused, monkeypatch):
         assert np.array_equal(logits[r], logits[0])
     for e in engines:
         e.close()
+
+
+def test_tp_engine_70b_rank_widths(hb, worlds):
+    """One layer at the Llama-3.1-70B widths (hidden 8192, 64/8 heads, FFN 28672) sharded over
+    the ranks, B = 128 as the benchmark runs it: at R ranks every projection, the attention
+    and the exchange have the per-rank shapes of TP = R (vocabulary cut to 4096 to keep the
+    oracle's lm_head small; its full width is covered on one GPU)."""
+    from oracle import llama_ref as R_
+
+    R = len(worlds)
+    shape = dict(hidden_size=8192, intermediate_size=28672, num_hidden_layers=1, num_attention_heads=64,
+                 num_key_value_heads=8, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+    B, plen = 128, 3
+    engines = on_all(worlds, lambda r, w: hb.Engine.create_random(shape, seed=5, norm_ones=True, max_seq_len=32,
+                                                                   bf16=True, tensor_parallel_size=R, world=w, max_batch=B))
+    cfg = R_.LlamaTpConfig(**shape)
+    oracle = R_.LlamaTpOracle(cfg, gather_llama_weights(engines, cfg, R_), world_size=R, dtype="bf16",
+                              reference_reduce=False, weights_exact=True)
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, plen)).astype(np.uint32)
+    seqs = on_all(worlds, lambda r, w: [engines[r].create_kv_cache() for _ in range(B)])
+    logits = [np.empty((B, cfg.vocab_size), dtype=np.float32) for _ in range(R)]
+    for t in range(plen):
+        run_lockstep(engines, seqs, prompts[:, t], logits)
+    hidden = np.stack([oracle.forward(prompts[i].tolist(), 0, oracle.new_cache(), logits=False)[-1] for i in range(16)])
+    want = oracle.final_logits(hidden)
+    for r in range(R):
+        err = float(np.max(np.abs(logits[r][:16] - want))) / float(np.max(np.abs(want)))
+        assert err <= 2e-2, (r, err)
+        assert np.array_equal(logits[r], logits[0])
+    for e in engines:
+        e.close()
+
+
+def test_tp_mixtral_matches_oracle(hb, worlds):
+    """Sparse mixture of experts, tensor-parallel over every expert's intermediate size: the
+    expert down projections leave through the same exchange as a dense FFN
+    (src/engine/arch/mixtral.rs:371-430 sharded as src/parallel/shard.rs:46-74)."""
+    from oracle import mixtral_ref as M
+
+    R = len(worlds)
+    shape = dict(hidden_size=1024, intermediate_size=256 * R, num_hidden_layers=2, num_attention_heads=8,
+                 num_key_value_heads=8, vocab_size=1024, rms_norm_eps=1e-5, rope_theta=1e6,
+                 num_local_experts=4, num_experts_per_tok=2, sliding_window=4096)
+    B, plen = 8, 6
+    engines = on_all(worlds, lambda r, w: hb.Engine.create_random(shape, seed=2, std=0.05, norm_ones=True, max_seq_len=64,
+                                                                   bf16=True, tensor_parallel_size=R, world=w, max_batch=B))
+    cfg = M.MixtralConfig(**shape)
+    weights = {}
+    for name, shp in M.tensor_shapes(cfg).items():
+        pieces = [engines[r].get_tensor(name) for r in range(R)]
+        if name.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "w1.weight", "w3.weight")):
+            weights[name] = np.concatenate([p.reshape(shp[0] // R, shp[1]) for p in pieces], 0)
+        elif name.endswith(("o_proj.weight", "w2.weight")):
+            weights[name] = np.concatenate([p.reshape(shp[0], shp[1] // R) for p in pieces], 1)
+        else:
+            weights[name] = pieces[0].reshape(shp)
+    oracle = M.MixtralOracle(cfg, weights, world_size=R, dtype="bf16")
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(B, plen)).astype(np.uint32)
+    seqs = on_all(worlds, lambda r, w: [engines[r].create_kv_cache() for _ in range(B)])
+    logits = [np.empty((B, cfg.vocab_size), dtype=np.float32) for _ in range(R)]
+    for t in range(plen):
+        run_lockstep(engines, seqs, prompts[:, t], logits)
+    want, gaps = [], []
+    for i in range(B):
+        oracle.min_route_gap = float("inf")
+        want.append(oracle.forward(prompts[i].tolist(), 0, oracle.new_cache()))
+        gaps.append(oracle.min_route_gap)
+    want, clear = np.stack(want), np.array(gaps) > 2e-2   # a top-2 choice inside bf16 noise may legally differ
+    assert clear.sum() >= B // 2
+    for r in range(R):
+        err = float(np.max(np.abs(logits[r][clear] - want[clear]))) / float(np.max(np.abs(want[clear])))
+        assert err <= 2e-2, (r, err, gaps)
+        assert np.array_equal(logits[r], logits[0])
+    for e in engines:
+        e.close()
+
+
+def test_nccl_baseline_all_reduce(hb, worlds):
+    """HB_ALGO_NCCL, the reference's own path (src/parallel/comm.rs:83-166), through this
+    library's entry point: same sums as the rank-order oracle within a rounding step."""
+    R = len(worlds)
+    uid = hb.TpWorld.nccl_unique_id()
+    errs = []
+
+    def init(r):
+        try:
+            with torch.cuda.device(worlds[r].device()):
+                worlds[r].init_nccl(uid)
+        except Exception as e:
+            errs.append((r, e))
+
+    ths = [threading.Thread(target=init, args=(r,)) for r in range(R)]  # communicator init is collective
+    [th.start() for th in ths]
+    [th.join() for th in ths]
+    assert not errs, errs
+    for dtype, count in (("f32", 4096), ("bf16", 128 * 8192)):
+        rng = np.random.default_rng(count)
+        shards = [K.rnd(rng.standard_normal(count).astype(np.float32), dtype) for _ in range(R)]
+        bufs = on_all(worlds, lambda r, w: torch.from_numpy(shards[r]).to(f"cuda:{w.device()}", TORCH[dtype]))
+        def reduce(r):
+            with torch.cuda.device(worlds[r].device()):
+                worlds[r].all_reduce(bufs[r], hb.ALGO_NCCL)
+
+        ths = [threading.Thread(target=reduce, args=(r,)) for r in range(R)]
+        [th.start() for th in ths]
+        [th.join() for th in ths]
+        for w in worlds:
+            torch.cuda.synchronize(w.device())
+        want = P.all_reduce_f32(shards, dtype)
+        tol = {"f32": 1e-5, "bf16": 2e-2}[dtype] * max(float(np.max(np.abs(want))), 1.0)
+        for r in range(R):
+            assert float(np.max(np.abs(host(bufs[r]) - want))) <= tol, (dtype, r)
+
+
+def test_wait_runs_out_and_the_context_survives(hb):
+    """Failure made on the host: of a fresh two-rank world only rank 0 launches the exchange,
+    with a poll limit of a few thousand.  The kernel must return, the status word must read
+    HB_ERR_TIMEOUT once and then clear, and new worlds on the same GPUs must work."""
+    if hb.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    ws = hb.TpWorld.new_local(2, staging_bytes=8 << 20)
+    try:
+        for w in ws:
+            w.set_wait_limit(4000)
+        M, N = 8, 4096
+        with torch.cuda.device(ws[0].device()):
+            dev = f"cuda:{ws[0].device()}"
+            part = torch.ones(M, N, device=dev, dtype=torch.bfloat16)
+            resid = torch.ones(M, N, device=dev, dtype=torch.bfloat16)
+            nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+            ws[0].all_reduce_add_rms_norm(part, resid, nw, 1e-5, hb.ALGO_ONE_SHOT)   # rank 1 never calls
+            torch.cuda.synchronize()
+            assert ws[0].status() == hb.ERR_TIMEOUT
+            assert ws[0].status() == 0                                            # reading clears it
+            ws[0].all_reduce(part.view(-1), hb.ALGO_ONE_SHOT)                     # the plain all-reduce kernel too
+            torch.cuda.synchronize()
+            assert ws[0].status() == hb.ERR_TIMEOUT
+    finally:
+        for w in ws:
+            w.close()
+    fresh = hb.TpWorld.new_local(2, staging_bytes=8 << 20)
+    try:
+        bufs = on_all(fresh, lambda r, w: torch.full((4096,), float(r + 1), device=f"cuda:{w.device()}"))
+        on_all(fresh, lambda r, w: w.all_reduce(bufs[r]))
+        for b in bufs:
+            assert float(b[0]) == 3.0 and float(b[-1]) == 3.0
+        assert all(w.status() == 0 for w in fresh)
+    finally:
+        for w in fresh:
+            w.close()

@@ -123,9 +123,12 @@ _SIGS = {
     "hb_world_staging_bytes": (_sz, [_vp]),
     "hb_world_stream": (_vp, [_vp]),
     "hb_world_status": (_i, [_vp]),
+    "hb_world_set_wait_limit": (_i, [_vp, C.c_uint32]),
+    "hb_world_set_early_trigger": (_i, [_vp, _i]),
     "hb_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i]),
     "hb_all_reduce_add_rms_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i]),
     "hb_fused_rowparallel_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "hb_fused_rowparallel_form": (_i, [_vp, _i64, _i64, _i64, _i]),
     "hb_fused_rowparallel": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f, _i, _vp]),
     "hb_column_shard": (_i, [_vp, _vp, _i64, _i64, _sz, _i, _i]),
     "hb_row_shard": (_i, [_vp, _vp, _i64, _i64, _sz, _i, _i]),
@@ -506,6 +509,13 @@ class TpWorld:
     def status(self) -> int:
         return lib.hb_world_status(self.handle)
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls after which a device-side wait on a peer flag gives up (0 = default)."""
+        check(lib.hb_world_set_wait_limit(self.handle, polls))
+
+    def set_early_trigger(self, on: bool) -> None:
+        check(lib.hb_world_set_early_trigger(self.handle, 1 if on else 0))
+
     def all_reduce(self, buf, algo: int = ALGO_AUTO, stream=None):
         """In-place SUM over ranks of a torch CUDA tensor (TpWorld::all_reduce)."""
         check(lib.hb_all_reduce(self.handle, _stream(stream), _ptr(buf), buf.numel(),
@@ -564,6 +574,15 @@ def fused_rowparallel(world, x, w, resid, norm_w, eps: float, algo: int = ALGO_A
                                    _ptr(res), _ptr(x), _ptr(w), _ptr(resid), _ptr(norm_w), M, N, Kl, float(eps),
                                    algo, _ptr(ws)))
     return normed, res
+
+
+ROWPAR_FORMS = {0: "single", 1: "push", 2: "exchange", 3: "nccl"}
+
+
+def fused_rowparallel_form(world, M: int, N: int, K_local: int, algo: int = ALGO_AUTO) -> str:
+    """Which form fused_rowparallel takes for this world, shape and algo."""
+    return ROWPAR_FORMS[check(lib.hb_fused_rowparallel_form(world.handle if world is not None else None, M, N,
+                                                            K_local, algo))]
 
 
 # ---------------------------------------------------------------- scheduler mirror

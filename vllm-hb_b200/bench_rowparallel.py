@@ -1,21 +1,21 @@
-"""Micro-benchmark of the fused row-parallel projection (GEMM + all-reduce + residual +
-RMSNorm) against the unfused sequences, one rank per GPU:
+"""Micro-benchmark of the row-parallel projection + all-reduce + residual + RMSNorm against
+the reference's sequence of library calls, one rank per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node TP --master-addr 127.0.0.1 \
-        --master-port 29500 vllm-hb_b200/bench_rowparallel.py [--iters 100] [--out FILE]
+        --master-port 29500 vllm-hb_b200/bench_rowparallel.py [--out FILE]
 
 Shapes: X [M, K/TP] ~N(0,1), W [N, K/TP] ~N(0,0.02) per rank, residual [M, N] ~N(0,1),
 norm weight ones, eps 1e-5; M in {1, 8, 64, 256}; (K, N) = (28672, 8192) (down_proj) and
-(8192, 8192) (o_proj).  Variants timed per point:
-    fused      hb_fused_rowparallel (auto / one-shot / two-shot)
-    gemm_arn   hb_gemm -> hb_all_reduce_add_rms_norm (one peer-memory kernel: what the engine runs)
-    unfused    hb_gemm -> hb_all_reduce (peer memory) -> hb_add_rms_norm
-    baseline   torch.matmul (cuBLAS) -> NCCL all_reduce -> hb_add_rms_norm: the
-               reference's sequence (src/engine/arch/llama_tp.rs:327,533-552)
-    baseline_eager  the same with the add and the norm as the reference ships them for bf16:
-               six eager elementwise launches (src/kernels/rms_norm.rs:128-132)
-Device time with CUDA events on the launching stream, max over ranks, weights rotated
-over 4 buffers so that they come from HBM, not L2.
+(8192, 8192) (o_proj).  Arms, each CAPTURED IN A CUDA GRAPH of at least 24 calls that
+rotate over enough weight buffers to exceed L2, so that neither arm pays host dispatch
+per call and the weights come from HBM:
+    fused     hb_fused_rowparallel (HB_ALGO_AUTO: the form hb_fused_rowparallel_form names)
+    baseline  cuBLAS GEMM (torch.matmul) -> hb_all_reduce(HB_ALGO_NCCL) -> hb_add_rms_norm:
+              the reference's sequence (src/engine/arch/llama_tp.rs:327,533-552,
+              src/parallel/comm.rs:83-166)
+Device time with CUDA events around the graph replays, max over ranks; roofline =
+max(HBM bytes / measured peak, NVLink bytes per direction / 770 GB/s).
+`run_points` is also what bench.py calls at N > 1.
 """
 from __future__ import annotations
 
@@ -25,18 +25,106 @@ import os
 import sys
 from pathlib import Path
 
-import torch
-import torch.distributed as dist
-
 ROOT = Path(__file__).resolve().parent.parent
-sys.path.insert(0, str(ROOT))
-import __graft_entry__ as entry  # noqa: E402
+NVLINK_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
+L2_BYTES = 126 << 20
+
+
+def run_points(hb, tp, rank: int, world: int, dev, hbm_gbs: float, ms=(1, 8, 64, 256),
+               shapes=((28672, 8192), (8192, 8192)), replays: int = 4, check: bool = True) -> list:
+    """One row per (K, N, M).  `tp` is this rank's TpWorld with its NCCL communicator
+    initialised (world > 1) or None."""
+    import torch
+    import torch.distributed as dist
+
+    rows = []
+    side = torch.cuda.Stream(device=dev)
+    for K, N in shapes:
+        Kl = K // world
+        w_bytes = N * Kl * 2
+        n_sets = max(4, -(-int(1.25 * L2_BYTES) // w_bytes))
+        calls = max(24, 3 * n_sets)
+        g = torch.Generator(device=dev).manual_seed(3 + rank)
+        ws = [(torch.randn(N, Kl, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(n_sets)]
+        nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+        for M in ms:
+            x = torch.randn(M, Kl, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
+            resid = torch.randn(M, N, generator=torch.Generator(device=dev).manual_seed(4), device=dev).to(torch.bfloat16)
+            fws = hb.fused_rowparallel_workspace(x, ws[0])
+            out_f = (torch.empty(M, N, device=dev, dtype=torch.bfloat16), torch.empty(M, N, device=dev, dtype=torch.bfloat16))
+            out_b = (torch.empty(M, N, device=dev, dtype=torch.bfloat16), torch.empty(M, N, device=dev, dtype=torch.bfloat16))
+            part = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+            def fused(i):
+                hb.fused_rowparallel(tp, x, ws[i], resid, nw, 1e-5, hb.ALGO_AUTO, workspace=fws, out=out_f)
+
+            def baseline(i):
+                st = torch.cuda.current_stream().cuda_stream
+                torch.matmul(x, ws[i].t(), out=part)
+                if tp is not None:
+                    hb.check(hb.lib.hb_all_reduce(tp.handle, st, part.data_ptr(), part.numel(), hb.BF16, hb.ALGO_NCCL))
+                hb.check(hb.lib.hb_add_rms_norm(st, out_b[0].data_ptr(), out_b[1].data_ptr(), part.data_ptr(),
+                                                resid.data_ptr(), nw.data_ptr(), M, N, 1e-5, hb.BF16))
+
+            def graph_time(fn):
+                # eager warm-up (one-time attribute and library set-up must not fall into the capture)
+                with torch.cuda.stream(side):
+                    for i in range(3):
+                        fn(i % n_sets)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(calls):
+                        fn(i % n_sets)
+                with torch.cuda.stream(side):
+                    graph.replay()
+                    side.synchronize()
+                    if world > 1:
+                        dist.barrier()
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(side)
+                    for _ in range(replays):
+                        graph.replay()
+                    b.record(side)
+                    side.synchronize()
+                t = torch.tensor([a.elapsed_time(b) * 1e3 / (replays * calls)], device=dev, dtype=torch.float64)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                del graph
+                return float(t)
+
+            row = {"M": M, "K": K, "N": N, "tp": world, "form": hb.fused_rowparallel_form(tp, M, N, Kl, hb.ALGO_AUTO),
+                   "weight_sets": n_sets, "calls_per_graph": calls}
+            row["fused_us"] = graph_time(fused)
+            row["baseline_us"] = graph_time(baseline)
+            row["ratio"] = row["baseline_us"] / row["fused_us"]
+            hbm_bytes = 2 * (Kl * N + M * Kl + 3 * M * N + N)
+            nvl_bytes = 2 * (world - 1) / world * 2 * M * N if world > 1 else 0
+            row["roofline_us"] = max(hbm_bytes / hbm_gbs / 1e3, nvl_bytes / NVLINK_GBS / 1e3)
+            row["frac_of_roofline"] = row["roofline_us"] / row["fused_us"]
+            if check:
+                # both arms ran the same inputs last (weight set (calls-1) % n_sets): same sums up to
+                # the order of the additions and one bf16 rounding of the partials
+                diff = (out_f[1].float() - out_b[1].float()).abs().max() / out_b[1].float().abs().max()
+                t = torch.tensor([float(diff)], device=dev, dtype=torch.float64)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                row["max_rel_diff_resid"] = float(t)
+            if tp is not None:
+                row["status"] = tp.status()
+            rows.append(row)
+    return rows
 
 
 def main() -> None:
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+
     ap = argparse.ArgumentParser()
-    ap.add_argument("--iters", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--out", default="")
     ap.add_argument("--ms", default="1,8,64,256")
     args = ap.parse_args()
@@ -47,101 +135,14 @@ def main() -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    tp = hb.TpWorld.from_torch_distributed(local, staging_bytes=96 << 20) if world > 1 else None
+    tp = hb.TpWorld.from_torch_distributed(local, staging_bytes=96 << 20, nccl=True) if world > 1 else None
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
-    hbm = float(peaks.get("hbm_gbs", 6650.0))
-    nvl = 770.0  # measured peer copy GB/s per direction on this pool (nominal 900)
-    results = []
-
-    def timed(fn, nbuf):
-        for i in range(args.warmup):
-            fn(i % nbuf)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(args.iters):
-            fn(i % nbuf)
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) * 1e3 / args.iters], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    for K, N in ((28672, 8192), (8192, 8192)):
-        Kl = K // world
-        g = torch.Generator(device=dev).manual_seed(3 + rank)
-        ws = [(torch.randn(N, Kl, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]
-        nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
-        for M in [int(m) for m in args.ms.split(",")]:
-            gx = torch.Generator(device=dev).manual_seed(2)
-            x = torch.randn(M, Kl, generator=gx, device=dev).to(torch.bfloat16)
-            resid = torch.randn(M, N, generator=torch.Generator(device=dev).manual_seed(4), device=dev).to(torch.bfloat16)
-            fws = hb.fused_rowparallel_workspace(x, ws[0])
-            out = (torch.empty(M, N, device=dev, dtype=torch.bfloat16), torch.empty(M, N, device=dev, dtype=torch.bfloat16))
-            part = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            gws = torch.zeros(max(hb.lib.hb_gemm_workspace_bytes(M, N, Kl, hb.BF16), 16), dtype=torch.uint8, device=dev)
-            st = torch.cuda.current_stream().cuda_stream
-
-            def fused(algo):
-                return lambda i: hb.fused_rowparallel(tp, x, ws[i], resid, nw, 1e-5, algo, workspace=fws, out=out)
-
-            def unfused(i):
-                hb.check(hb.lib.hb_gemm(st, part.data_ptr(), x.data_ptr(), ws[i].data_ptr(), M, N, Kl, hb.BF16, gws.data_ptr()))
-                if tp is not None:
-                    tp.all_reduce(part)
-                hb.check(hb.lib.hb_add_rms_norm(st, out[0].data_ptr(), out[1].data_ptr(), part.data_ptr(), resid.data_ptr(),
-                                                nw.data_ptr(), M, N, 1e-5, hb.BF16))
-
-            def gemm_arn(i):
-                hb.check(hb.lib.hb_gemm(st, part.data_ptr(), x.data_ptr(), ws[i].data_ptr(), M, N, Kl, hb.BF16, gws.data_ptr()))
-                hb.check(hb.lib.hb_all_reduce_add_rms_norm(tp.handle, st, out[0].data_ptr(), out[1].data_ptr(), part.data_ptr(),
-                                                           resid.data_ptr(), nw.data_ptr(), M, N, 1e-5, hb.BF16, hb.ALGO_AUTO))
-
-            def baseline(i):
-                p2 = torch.matmul(x, ws[i].t())
-                if world > 1:
-                    dist.all_reduce(p2)
-                hb.check(hb.lib.hb_add_rms_norm(st, out[0].data_ptr(), out[1].data_ptr(), p2.data_ptr(), resid.data_ptr(),
-                                                nw.data_ptr(), M, N, 1e-5, hb.BF16))
-
-            def baseline_eager(i):
-                p2 = torch.matmul(x, ws[i].t())
-                if world > 1:
-                    dist.all_reduce(p2)
-                h = resid + p2
-                var = h.pow(2).mean(-1, keepdim=True) + 1e-5
-                out[0].copy_(h / var.sqrt() * nw)
-
-            row = {"K": K, "N": N, "M": M, "tp": world}
-            row["fused_auto_us"] = timed(fused(hb.ALGO_AUTO), 4)
-            if world > 1:
-                row["fused_one_shot_us"] = timed(fused(hb.ALGO_ONE_SHOT), 4)
-                row["fused_two_shot_us"] = timed(fused(hb.ALGO_TWO_SHOT), 4)
-            if world > 1:
-                row["gemm_arn_us"] = timed(gemm_arn, 4)
-            row["unfused_us"] = timed(unfused, 4)
-            row["baseline_cublas_nccl_us"] = timed(baseline, 4)
-            row["baseline_eager_norm_us"] = timed(baseline_eager, 4)
-            hbm_bytes = 2 * (Kl * N + M * Kl + 3 * M * N + N)
-            nvl_bytes = 2 * (world - 1) / world * 2 * M * N if world > 1 else 0
-            row["hbm_bytes"], row["nvlink_bytes_per_dir"] = hbm_bytes, nvl_bytes
-            roof_us = max(hbm_bytes / hbm / 1e3, nvl_bytes / nvl / 1e3)
-            row["roofline_us"] = roof_us
-            best = min(v for k, v in row.items() if k.startswith("fused_") or k == "gemm_arn_us")
-            row["best_frac_of_roofline"] = roof_us / best
-            row["speedup_vs_baseline"] = row["baseline_cublas_nccl_us"] / best
-            row["speedup_vs_unfused"] = row["unfused_us"] / best
-            if tp is not None and tp.status() != 0:
-                row["status"] = tp.status()
-            results.append(row)
-            if rank == 0:
-                print(json.dumps(row), flush=True)
-    if rank == 0 and args.out:
-        Path(args.out).write_text(json.dumps(results, indent=1))
+    rows = run_points(hb, tp, rank, world, dev, float(peaks.get("hbm_gbs", 6650.0)), ms=[int(m) for m in args.ms.split(",")])
+    if rank == 0:
+        for r in rows:
+            print(json.dumps(r), flush=True)
+        if args.out:
+            Path(args.out).write_text(json.dumps(rows, indent=1))
     if tp is not None:
         torch.cuda.synchronize()
         dist.barrier()

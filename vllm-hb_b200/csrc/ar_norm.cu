@@ -15,11 +15,14 @@
 // per-rank "done" flags guarding the staging area):
 //   one-shot : every rank pushes row r of its partial to every peer; every rank reduces
 //              and normalises every row.
-//   two-shot : row r is reduced by rank r % R only, which pushes the new residual row to
-//              its peers; every rank then normalises the row it received.
+//   two-shot : rank q reduces the q-th column slice of EVERY row (each row's CTA pushes the
+//              other R-1 slices of its partial to their reducers, sums its own slice, pushes
+//              the result to its peers and collects theirs); every rank then normalises the
+//              full row.  All CTAs of all ranks do the same amount of work in both hops.
 // Every wait is bounded; on expiry the kernel records HB_ERR_TIMEOUT in the world's status
 // word and returns.
 #include "comm.h"
+#include "peer_sync.cuh"
 
 #include <cstring>
 
@@ -30,22 +33,10 @@ namespace hb {
 // bit-identical to hb_add_rms_norm's.
 constexpr int kAnThreads = 256;
 constexpr int kAnMaxVec = 8;  // 16-byte vectors per thread kept in registers
-constexpr uint32_t kAnSpin = 1u << 22;
 
-__device__ __forceinline__ uint32_t an_ld_acquire(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void an_st_release(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ bool an_wait_ge(const uint32_t* p, uint32_t target) {
-  for (uint32_t it = 0; it < kAnSpin; ++it) {
-    if ((int32_t)(an_ld_acquire(p) - target) >= 0) return true;
-    if (it > 64) __nanosleep(40);
-  }
-  return false;
+__device__ __forceinline__ void an_st_release(uint32_t* p, uint32_t v) { peer_st_release(p, v); }
+__device__ __forceinline__ bool an_wait_ge(const uint32_t* p, uint32_t target, uint32_t limit) {
+  return peer_wait_ge(p, target, limit);
 }
 
 // Optional phase timestamps (compiled in with -DHB_TC_TRACE only): the CTA of one row this
@@ -76,17 +67,31 @@ struct ArNormParams {
   int ws, rank, two_shot;
   int M;
   int64_t row_vecs;      // N * sizeof(T) / 16
-  int rows_own;          // two-shot: rows a rank reduces = ceil(M / R); one-shot: M
+  int64_t slice_vecs;    // two-shot: vectors of every row one rank reduces = ceil(row_vecs / R)
   int64_t gather_off;    // two-shot: vector offset of the gathered rows inside the data area
   float eps;
   float n_feat;
   int pdl;               // let the next kernel of the stream start its prologue while this one waits for peers
+  uint32_t spin;         // polls before a wait gives up
+  // staged != 0 (two-shot only): the partial slices are already on their way into the
+  // reducers' staging, pushed by the epilogue of the GEMM that computed them (gemm_tc.cu,
+  // kEpiPush), one 128-feature tile of `row_block` batch rows at a time; the arrival of
+  // tile ti of the slice from rank src for row block b is tflag[(b * R + src) * tiles + ti].
+  int staged, row_block, tiles_per_slice;
 };
 
 // VPT = 16-byte vectors per thread (row_vecs <= VPT * kAnThreads).  Everything a CTA needs
 // that does not come from a peer (its partial row, the residual row, the norm weight) is
-// requested before the first wait and arrives while the CTA waits; the staged rows of the
-// peers are read with all loads of a source in flight together.
+// requested before the first wait and arrives while the CTA waits; the staged vectors of
+// the peers are read with all loads in flight together.
+//
+// Staging (data area of every rank, same offsets everywhere):
+//   one-shot : [source rank][row][row_vecs]
+//   two-shot : [source rank][row][slice_vecs]  partial slices pushed to their reducer,
+//              then at gather_off [row][row_vecs] the reduced slices pushed back.
+// Two-shot splits every row by COLUMNS: rank q reduces vectors [q*slice_vecs, (q+1)*slice_vecs)
+// of all rows, so the CTA of a row does 1/R of that row's summing on every rank (none idles
+// while a few reduce whole rows) and each hop moves slice-sized messages between all pairs.
 template <typename T, int VPT>
 __global__ void __launch_bounds__(kAnThreads)
 ar_add_norm_kernel(const ArNormParams p) {
@@ -94,7 +99,7 @@ ar_add_norm_kernel(const ArNormParams p) {
   __shared__ uint32_t s_seq;
   __shared__ float s_red[33];
   // Most of this kernel is waiting for peers.  The next kernel of the stream (a GEMM that
-  // prefetches its weights before its own dependency wait) may become resident meanwhile.
+  // requests its weights before its own dependency wait) may become resident meanwhile.
   // This grid itself touches nothing, the sequence number included, before every earlier
   // kernel of the stream has completed.
   if (p.pdl) pdl_trigger();
@@ -103,13 +108,12 @@ ar_add_norm_kernel(const ArNormParams p) {
   CommFlags* fl = reinterpret_cast<CommFlags*>(p.peer[me]);
   auto flags_of = [&](int q) { return reinterpret_cast<CommFlags*>(p.peer[q]); };
   auto data_of = [&](int q) { return reinterpret_cast<uint4*>((uint8_t*)p.peer[q] + kFlagBytes); };
-  const int64_t rv = p.row_vecs;
+  const int64_t rv = p.row_vecs, sv = p.slice_vecs;
   const uint4* part = reinterpret_cast<const uint4*>(p.partial) + (int64_t)row * rv;
   const uint4* rin = reinterpret_cast<const uint4*>(p.resid_in) + (int64_t)row * rv;
   uint4* rout = reinterpret_cast<uint4*>(p.resid_out) + (int64_t)row * rv;
-  const int owner = p.two_shot ? row % R : me;
-  const int slot = p.two_shot ? row / R : row;
-  const bool reducer = owner == me;
+  // owner of vector v: everybody reduces everything (one-shot) or the slice's rank (two-shot)
+  auto mine_to_reduce = [&](int64_t v) { return !p.two_shot || (int)(v / sv) == me; };
 
   uint4 pv[VPT], rr[VPT], wv[VPT];
 #pragma unroll
@@ -117,8 +121,8 @@ ar_add_norm_kernel(const ArNormParams p) {
     const int64_t v = tid + (int64_t)i * kAnThreads;
     pv[i] = rr[i] = wv[i] = make_uint4(0, 0, 0, 0);
     if (v < rv) {
-      pv[i] = part[v];
-      if (reducer) rr[i] = rin[v];
+      if (!p.staged) pv[i] = part[v];
+      if (mine_to_reduce(v)) rr[i] = rin[v];
       if (p.normed_out) wv[i] = reinterpret_cast<const uint4*>(p.norm_w)[v];
     }
   }
@@ -132,105 +136,128 @@ ar_add_norm_kernel(const ArNormParams p) {
   AN_TRACE(0);
 
   // A. peers must be done with the previous collective before their staging is written
+  // (staged: the GEMM epilogue waited for that before it pushed)
   bool ok = true;
-  if (tid < R && tid != me) ok = an_wait_ge(&fl->done[tid], seq);
+  if (!p.staged && tid < R && tid != me) ok = an_wait_ge(&fl->done[tid], seq, p.spin);
   bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   AN_TRACE(1);
 
-  // B. push this rank's partial row to its reducer(s)
-  if (all_ok) {
-    for (int q = 0; q < R; ++q) {
-      if (q == me || (p.two_shot && q != owner)) continue;
-      uint4* dst = data_of(q) + ((int64_t)me * p.rows_own + slot) * rv;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int64_t v = tid + (int64_t)i * kAnThreads;
-        if (v < rv) dst[v] = pv[i];
-      }
-    }
-    __syncthreads();  // orders every thread's stores before the flag threads' release stores
-    if (tid < R && tid != me && (!p.two_shot || tid == owner))
-      an_st_release(&flags_of(tid)->pflag[row * HB_MAX_RANKS + me], target);
-  }
-  AN_TRACE(2);
-
-  // C. the new residual row, kept in registers
-  uint4 hv[VPT];
-  if (all_ok && reducer) {
-    ok = true;
-    if (tid < R && tid != me) ok = an_wait_ge(&fl->pflag[row * HB_MAX_RANKS + tid], target);
-    all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
-    AN_TRACE(3);
-    if (all_ok) {
-      const uint4* mine = data_of(me) + (int64_t)slot * rv;
-      const int64_t src_stride = (int64_t)p.rows_own * rv;
-      float acc[VPT][N];
-#pragma unroll
-      for (int i = 0; i < VPT; ++i)
-#pragma unroll
-        for (int j = 0; j < N; ++j) acc[i][j] = 0.f;
-      // fp32 sum in rank order, this rank's own partial in its place
-#pragma unroll(VPT >= 8 ? 2 : 4)
-      for (int src = 0; src < R; ++src) {
-        uint4 x[VPT];
+  // B. push this rank's partial row: all of it to every peer (one-shot), each slice to its
+  // reducer (two-shot)
+  if (all_ok && !p.staged) {
+    if (!p.two_shot) {
+      for (int q = 0; q < R; ++q) {
+        if (q == me) continue;
+        uint4* dst = data_of(q) + ((int64_t)me * p.M + row) * rv;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int64_t v = tid + (int64_t)i * kAnThreads;
-          x[i] = pv[i];
-          if (src != me && v < rv) x[i] = __ldcg(mine + src * src_stride + v);
-        }
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const T* e = reinterpret_cast<const T*>(&x[i]);
-#pragma unroll
-          for (int j = 0; j < N; ++j) acc[i][j] += to_f32<T>(e[j]);
+          if (v < rv) dst[v] = pv[i];
         }
       }
+    } else {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int64_t v = tid + (int64_t)i * kAnThreads;
-        const T* re = reinterpret_cast<const T*>(&rr[i]);
-        T* he = reinterpret_cast<T*>(&hv[i]);
-#pragma unroll
-        for (int j = 0; j < N; ++j) {
-          const float s = to_f32<T>(from_f32<T>(acc[i][j]));     // the all-reduce rounds once
-          he[j] = from_f32<T>(to_f32<T>(re[j]) + s);             // the sum is materialised in T
+        if (v < rv) {
+          const int q = (int)(v / sv);
+          if (q != me) data_of(q)[((int64_t)me * p.M + row) * sv + (v - (int64_t)q * sv)] = pv[i];
         }
-        if (v < rv) rout[v] = hv[i];
       }
-      if (p.two_shot) {
-        for (int q = 0; q < R; ++q) {
-          if (q == me) continue;
-          uint4* dst = data_of(q) + p.gather_off + (int64_t)row * rv;
+    }
+    __syncthreads();  // orders every thread's stores before the flag threads' release stores
+    if (tid < R && tid != me) an_st_release(&flags_of(tid)->pflag[row * HB_MAX_RANKS + me], target);
+  }
+  AN_TRACE(2);
+
+  // C. wait for the peers' partials of this row, sum what this rank reduces
+  uint4 hv[VPT];
 #pragma unroll
-          for (int i = 0; i < VPT; ++i) {
-            const int64_t v = tid + (int64_t)i * kAnThreads;
-            if (v < rv) dst[v] = hv[i];
+  for (int i = 0; i < VPT; ++i) hv[i] = make_uint4(0, 0, 0, 0);
+  if (all_ok) {
+    ok = true;
+    if (p.staged) {
+      // every tile of this rank's slice, from every rank (this one included)
+      const int n_flags = R * p.tiles_per_slice, b = row / p.row_block;
+      for (int f = tid; f < n_flags; f += kAnThreads) ok = ok && an_wait_ge(&fl->tflag[b * n_flags + f], target, p.spin);
+    } else if (tid < R && tid != me) {
+      ok = an_wait_ge(&fl->pflag[row * HB_MAX_RANKS + tid], target, p.spin);
+    }
+    all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  }
+  AN_TRACE(3);
+  if (all_ok) {
+    const uint4* mine = data_of(me);
+    // vector v of source rank `src` in this rank's staging
+    const int64_t src_stride = (int64_t)p.M * (p.two_shot ? sv : rv);
+    const int64_t row_off = (int64_t)row * (p.two_shot ? sv : rv) - (p.two_shot ? (int64_t)me * sv : 0);
+    // groups of at most four vectors per thread: all their staged loads are in flight together
+    constexpr int G = VPT < 4 ? VPT : 4;
+#pragma unroll
+    for (int i0 = 0; i0 < VPT; i0 += G) {
+      uint4 x[G][HB_MAX_RANKS];
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        const int i = i0 + gi;
+        const int64_t v = tid + (int64_t)i * kAnThreads;
+        const bool red = v < rv && mine_to_reduce(v);
+#pragma unroll
+        for (int src = 0; src < HB_MAX_RANKS; ++src) {
+          x[gi][src] = pv[i];
+          if (red && src < R && (src != me || p.staged)) x[gi][src] = __ldcg(mine + src * src_stride + row_off + v);
+        }
+      }
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        const int i = i0 + gi;
+        const int64_t v = tid + (int64_t)i * kAnThreads;
+        if (v < rv && mine_to_reduce(v)) {
+          // fp32 sum in rank order, this rank's own partial in its place
+          float acc[N];
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int src = 0; src < HB_MAX_RANKS; ++src) {
+            if (src < R) {
+              const T* e = reinterpret_cast<const T*>(&x[gi][src]);
+#pragma unroll
+              for (int j = 0; j < N; ++j) acc[j] += to_f32<T>(e[j]);
+            }
+          }
+          const T* re = reinterpret_cast<const T*>(&rr[i]);
+          T* he = reinterpret_cast<T*>(&hv[i]);
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            const float s = to_f32<T>(from_f32<T>(acc[j]));      // the all-reduce rounds once
+            he[j] = from_f32<T>(to_f32<T>(re[j]) + s);           // the sum is materialised in T
+          }
+          rout[v] = hv[i];
+          if (p.two_shot) {
+            // the reduced slice goes back to every peer
+            for (int q = 0; q < R; ++q)
+              if (q != me) data_of(q)[p.gather_off + (int64_t)row * rv + v] = hv[i];
           }
         }
-        __syncthreads();
-        if (tid < R && tid != me) an_st_release(&flags_of(tid)->gflag[row], target);
       }
-      AN_TRACE(4);
     }
-  } else if (all_ok) {
-    // D. two-shot, a row reduced elsewhere: wait for the gathered row
-    ok = true;
-    if (tid == 0) ok = an_wait_ge(&fl->gflag[row], target);
-    all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
-    AN_TRACE(3);
-    if (all_ok) {
-      const uint4* src = data_of(me) + p.gather_off + (int64_t)row * rv;
+    AN_TRACE(4);
+    if (p.two_shot) {
+      __syncthreads();
+      if (tid < R && tid != me) an_st_release(&flags_of(tid)->sflag[row * HB_MAX_RANKS + me], target);
+      // D. the slices of this row reduced elsewhere
+      ok = true;
+      if (tid < R && tid != me) ok = an_wait_ge(&fl->sflag[row * HB_MAX_RANKS + tid], target, p.spin);
+      all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
+      if (all_ok) {
+        const uint4* src = mine + p.gather_off + (int64_t)row * rv;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int64_t v = tid + (int64_t)i * kAnThreads;
-        hv[i] = make_uint4(0, 0, 0, 0);
-        if (v < rv) hv[i] = __ldcg(src + v);
-      }
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int64_t v = tid + (int64_t)i * kAnThreads;
-        if (v < rv) rout[v] = hv[i];
+        for (int i = 0; i < VPT; ++i) {
+          const int64_t v = tid + (int64_t)i * kAnThreads;
+          if (v < rv && !mine_to_reduce(v)) {
+            hv[i] = __ldcg(src + v);
+            rout[v] = hv[i];
+          }
+        }
       }
     }
   }
@@ -289,10 +316,17 @@ ar_add_norm_kernel(const ArNormParams p) {
 }
 
 template <typename T, int VPT>
-static cudaError_t launch_ar_add_norm(const ArNormParams& p, bool secondary, cudaStream_t st) {
-  if (secondary) return launch_pdl(ar_add_norm_kernel<T, VPT>, dim3((unsigned)p.M), dim3(kAnThreads), 0, st, p);
+static cudaError_t launch_ar_add_norm(const ArNormParams& p, cudaStream_t st) {
   ar_add_norm_kernel<T, VPT><<<(unsigned)p.M, kAnThreads, 0, st>>>(p);
   return cudaGetLastError();
+}
+
+bool push_exchange_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype) {
+  // bf16 rows whose rank slices are whole 128-feature GEMM tiles; staging for the pushed
+  // slices and the gathered rows
+  if (!ar_add_norm_supported(w, M, N, dtype) || dtype != HB_BF16) return false;
+  if (N % ((int64_t)w->ws * 128)) return false;
+  return (size_t)2 * M * N * 2 <= w->staging_bytes;
 }
 
 bool ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype) {
@@ -305,19 +339,27 @@ bool ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dty
 
 int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
                       const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
-                      hb_dtype dtype, hb_algo algo) {
+                      hb_dtype dtype, hb_algo algo, const PushGeometry* staged) {
   if (!ar_add_norm_supported(w, M, N, dtype))
     return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: unsupported shape %lld x %lld or world", (long long)M,
                 (long long)N);
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (staged) {
+    if (!push_exchange_supported(w, M, N, dtype) || staged->row_block < 1 || staged->tiles_per_slice < 1 ||
+        (int64_t)staged->tiles_per_slice * 128 * w->ws != N ||
+        ((M + staged->row_block - 1) / staged->row_block) * w->ws * staged->tiles_per_slice > kMaxPushFlags)
+      return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: bad geometry for partials pushed by the GEMM");
+  } else if (!partial) {
+    return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: null partial");
+  }
   if (!al16(partial) || !al16(resid_in) || !al16(resid_out) || !al16(normed_out) || !al16(norm_w))
     return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: buffers must be 16-byte aligned");
   if (normed_out && !norm_w) return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: normed_out needs a weight");
   HB_CUDA_CHECK(cudaSetDevice(w->device));
   const int R = w->ws;
   const size_t row_bytes = (size_t)N * dtype_size(dtype);
-  bool two = algo == HB_ALGO_TWO_SHOT;
-  if (algo == HB_ALGO_AUTO) two = R > 2 && (size_t)M * row_bytes > 128 * 1024;
+  bool two = algo == HB_ALGO_TWO_SHOT || staged;
+  if (algo == HB_ALGO_AUTO) two = staged || (R > 2 && (size_t)M * row_bytes > 128 * 1024);
   ArNormParams p;
   memset(&p, 0, sizeof(p));
   for (int q = 0; q < R; ++q) p.peer[q] = w->peer[q];
@@ -325,28 +367,29 @@ int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resi
   p.ws = R; p.rank = w->rank; p.two_shot = two ? 1 : 0;
   p.M = (int)M;
   p.row_vecs = (int64_t)(row_bytes / 16);
-  p.rows_own = two ? (int)((M + R - 1) / R) : (int)M;
-  p.gather_off = (int64_t)R * p.rows_own * p.row_vecs;
+  p.slice_vecs = two ? (p.row_vecs + R - 1) / R : p.row_vecs;
+  p.gather_off = (int64_t)R * M * p.slice_vecs;
   p.eps = eps;
   p.n_feat = (float)N;
-  // Programmatic edges around this kernel measured slower than full serialisation inside
-  // the decode graph (70B shape, 2 ranks, 40 layers: 10.85 ms serialised, 10.89 with the
-  // edge to the next kernel, 11.05 with the edge from the previous one, 11.15 with both),
-  // so they are opt-in.  HB_AR_PDL: 0 = serialised (default), 1 = both edges, 2 = only the
-  // edge to the next kernel, 3 = only the edge from the previous one.
-  static const int mode = [] { const char* e = getenv("HB_AR_PDL"); return e ? atoi(e) : 0; }();
-  const bool secondary = pdl_enabled() && (mode == 1 || mode == 3);
-  p.pdl = pdl_enabled() && (mode == 1 || mode == 2) ? 1 : 0;
+  p.spin = w->wait_limit;
+  if (staged) {
+    p.staged = 1;
+    p.row_block = staged->row_block;
+    p.tiles_per_slice = staged->tiles_per_slice;
+  }
+  // The successor may become resident while this kernel waits for its peers: a GEMM then
+  // requests its weights into shared memory and L2 during the exchange, when HBM is idle.
+  p.pdl = pdl_enabled() && w->trigger_early ? 1 : 0;
   const size_t need = ((size_t)p.gather_off + (two ? (size_t)M * p.row_vecs : 0)) * 16;
   if (need > w->staging_bytes)
     return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: needs %zu bytes of staging, world has %zu", need,
                 w->staging_bytes);
   const int64_t vpt = (p.row_vecs + kAnThreads - 1) / kAnThreads;
   HB_DISPATCH_DTYPE(dtype, T, {
-    if (vpt <= 1) HB_CUDA_CHECK((launch_ar_add_norm<T, 1>(p, secondary, st)));
-    else if (vpt <= 2) HB_CUDA_CHECK((launch_ar_add_norm<T, 2>(p, secondary, st)));
-    else if (vpt <= 4) HB_CUDA_CHECK((launch_ar_add_norm<T, 4>(p, secondary, st)));
-    else HB_CUDA_CHECK((launch_ar_add_norm<T, 8>(p, secondary, st)));
+    if (vpt <= 1) HB_CUDA_CHECK((launch_ar_add_norm<T, 1>(p, st)));
+    else if (vpt <= 2) HB_CUDA_CHECK((launch_ar_add_norm<T, 2>(p, st)));
+    else if (vpt <= 4) HB_CUDA_CHECK((launch_ar_add_norm<T, 4>(p, st)));
+    else HB_CUDA_CHECK((launch_ar_add_norm<T, 8>(p, st)));
   });
   return HB_OK;
 }
@@ -369,7 +412,7 @@ int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void
                                hb_dtype dtype, hb_algo algo) {
   HB_CHECK_ARG(w && resid_out && partial && resid_in, "hb_all_reduce_add_rms_norm: null argument");
   return hb::world_ar_add_norm(w, stream ? (cudaStream_t)stream : w->stream, normed_out, resid_out, partial, resid_in,
-                               norm_w, rows, hidden, eps, dtype, algo);
+                               norm_w, rows, hidden, eps, dtype, algo, nullptr);
 }
 
 }  // extern "C"

@@ -11,6 +11,7 @@
 // kernel combines by log-sum-exp.
 //
 // Pool layout per layer: [num_blocks, n_kv_heads, 16, head_dim].
+#include <climits>
 #include <cfloat>
 #include <mutex>
 
@@ -74,7 +75,9 @@ paged_attn_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __rest
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = lane % LPR, grp = lane / LPR;
 
-  const int ctx = ctx_lens[seq];
+  // a context longer than the table row can describe is cut to the row (the table of the
+  // next sequence, or memory past the allocation, is never indexed)
+  const int ctx = max(0, min(ctx_lens[seq], (int)min(max_blocks * HB_BLOCK_SIZE, (int64_t)INT_MAX)));
   const int nblk = (ctx + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
   // sliding window (src/engine/arch/mixtral.rs:155-176): keys ki with ctx-1-ki < window
   const int first_tok = window > 0 ? max(0, ctx - window) : 0;
@@ -314,8 +317,7 @@ bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* 
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int window, int* err_flag, const float* rope_inv_freq,
-                        int fresh);
+                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh);
 
 // Internal entry: q rows may sit inside a wider [q|k|v] projection buffer.  err_flag
 // (device int, may be null) is raised when a bounded wait of the tensor-core kernel ran out.
@@ -323,7 +325,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag, int window, const float* rope_inv_freq, int fresh_tokens) {
+                    hb_dtype dtype, int* err_flag, int window, int fresh_tokens) {
   if (n_seqs == 0) return HB_OK;
   const int nrep = n_q_heads / n_kv_heads;
   float* po = (float*)workspace;
@@ -332,7 +334,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
   if (!force_simt && paged_attention_mma_supported(q, q_stride, k_cache, v_cache, nrep, head_dim, num_blocks,
                                                    n_kv_heads, dtype)) {
     int rc = paged_attention_mma(st, out, po, pml, q, q_stride, k_cache, v_cache, block_tables, ctx_lens, n_seqs,
-                                 n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, window, err_flag, rope_inv_freq,
+                                 n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, window, err_flag,
                                  fresh_tokens);
     if (rc) return rc;
     if (n_splits > 1) {
@@ -342,8 +344,6 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
     }
     return HB_OK;
   }
-  if (rope_inv_freq)
-    return fail(HB_ERR_INVALID_ARG, "paged attention: the fused RoPE + KV append needs the tensor-core kernel");
   HB_DISPATCH_DTYPE(dtype, T, {
     if (head_dim == 128)
       return (dispatch_nrep<T, 128>(nrep, st, (T*)out, po, pml, (const T*)q, (const T*)k_cache,
@@ -383,7 +383,7 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
   HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention: bad block counts");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads,
-                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, 0, nullptr, -1);
+                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, 0, -1);
 }
 
 int hb_paged_decode_attention_window(void* stream, void* out, const void* q, const void* k_cache,
@@ -404,7 +404,7 @@ int hb_paged_decode_attention_window(void* stream, void* out, const void* q, con
   HB_CHECK_ARG(sliding_window >= 0, "hb_paged_decode_attention_window: negative window");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, sliding_window, nullptr, -1);
+                             max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, sliding_window, -1);
 }
 
 }  // extern "C"
@@ -469,7 +469,7 @@ int hb_paged_decode_attention_static(void* stream, void* out, const void* q, con
   if (rc) return rc;
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache, v_cache,
                              block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr, 0, nullptr, -1);
+                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr, 0, -1);
 }
 
 }  // extern "C"

@@ -23,6 +23,7 @@
 //
 // Every wait is bounded: on expiry the CTA raises *err_flag (when given), writes NaN
 // to its outputs, lets outstanding copies land and returns.
+#include <climits>
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -70,27 +71,27 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                       float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ q,
                       const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens, int hq,
                       int hkv, int nrep, int64_t max_blocks, int64_t num_blocks, int n_splits, float scale,
-                      int64_t q_stride, int window, int* err_flag, const float* __restrict__ rope_inv_freq,
-                      __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int fresh) {
+                      int64_t q_stride, int window, int* err_flag, int fresh) {
   constexpr int kMmaAttnWarps = NW, kMmaAttnThreads = NW * 32;
   pdl_trigger();
   // fresh >= 0: at most `fresh` tokens at the end of every sequence were written by the
   // kernels right before this one (the current step's K/V); every earlier block of the pool
   // is final, so its copies may start before those kernels have completed.  The context
   // lengths and block tables are step inputs, not products of a kernel.
-  const bool early = fresh >= 0 && rope_inv_freq == nullptr;
+  const bool early = fresh >= 0;
   if (!early) pdl_grid_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[kMmaAttnWarps][kAttnStages];
   __shared__ int s_abort;
-  __shared__ float s_cos[kAttnHD / 2], s_sin[kAttnHD / 2];
 
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int64_t seq = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;  // MMA fragment coordinates
 
-  const int ctx = ctx_lens[seq];
+  // a context longer than the table row can describe is cut to the row (the table of the
+  // next sequence, or memory past the allocation, is never indexed)
+  const int ctx = max(0, min(ctx_lens[seq], (int)min(max_blocks * HB_BLOCK_SIZE, (int64_t)INT_MAX)));
   const int nblk = (ctx + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
   // sliding window (src/engine/arch/mixtral.rs:155-176): the query at position ctx-1 sees
   // the keys ki with ctx-1-ki < window
@@ -111,40 +112,6 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     for (int s = 0; s < kAttnStages; ++s) mbar_init(smem_u32(&s_full[warp][s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  // ---- fused RoPE + KV append (rope_inv_freq != null): q points at rows [q | k | v] of the
-  // fused projection.  cos/sin of position ctx-1 in f32, rounded to bf16 as the reference
-  // casts its tables (src/engine/arch/llama_tp.rs:112-152); the rotated K row and the V row
-  // of the new token go to their slot of the pool before any block of it is fetched.
-  const bool fuse_rope = rope_inv_freq != nullptr;
-  if (fuse_rope) {
-    const float pos = (float)(ctx - 1);
-    for (int i = tid; i < kAttnHD / 2; i += kMmaAttnThreads) {
-      float sn, cs;
-      sincosf(pos * rope_inv_freq[i], &sn, &cs);
-      s_cos[i] = __bfloat162float(__float2bfloat16_rn(cs));
-      s_sin[i] = __bfloat162float(__float2bfloat16_rn(sn));
-    }
-  }
-  __syncthreads();
-  if (fuse_rope && b0 < b1 && b1 == nblk && ctx > 0) {
-    // exactly one split of a (sequence, kv head) reads the last block: it appends the token
-    int64_t phys = block_tables[seq * max_blocks + (ctx - 1) / HB_BLOCK_SIZE];
-    if (phys >= 0 && phys < num_blocks) {
-      const int64_t dst = ((phys * hkv + kvh) * HB_BLOCK_SIZE + (ctx - 1) % HB_BLOCK_SIZE) * kAttnHD;
-      const __nv_bfloat16* k_raw = q + seq * q_stride + ((int64_t)hq + kvh) * kAttnHD;
-      const __nv_bfloat16* v_raw = q + seq * q_stride + ((int64_t)hq + hkv + kvh) * kAttnHD;
-      for (int i = tid; i < kAttnHD / 2; i += kMmaAttnThreads) {
-        const float x1 = __bfloat162float(k_raw[i]), x2 = __bfloat162float(k_raw[i + kAttnHD / 2]);
-        const float c = s_cos[i], sn = s_sin[i];
-        k_pool[dst + i] = __float2bfloat16_rn(x1 * c - x2 * sn);
-        k_pool[dst + i + kAttnHD / 2] = __float2bfloat16_rn(x1 * sn + x2 * c);
-        reinterpret_cast<uint32_t*>(v_pool + dst)[i] = reinterpret_cast<const uint32_t*>(v_raw)[i];
-      }
-    }
-    // generic-proxy global writes above -> async-proxy (TMA) reads of the same block below
-    __threadfence();
-    asm volatile("fence.proxy.async;" ::: "memory");
   }
   __syncthreads();
 
@@ -201,21 +168,6 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       qa[ks][1] = h1 ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
       qa[ks][2] = h0 ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
       qa[ks][3] = h1 ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
-    }
-    if (fuse_rope) {
-      // the rotation pairs column c with c + 64: fragment registers [ks][r] and [ks + 4][r]
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int c = ks * 16 + 2 * t + (r >= 2 ? 8 : 0);
-          const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks][r]));
-          const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks + 4][r]));
-          const float c0 = s_cos[c], s0 = s_sin[c], c1 = s_cos[c + 1], s1 = s_sin[c + 1];
-          qa[ks][r] = pack_bf16(x1.x * c0 - x2.x * s0, x1.y * c1 - x2.y * s1);
-          qa[ks + 4][r] = pack_bf16(x1.x * s0 + x2.x * c0, x1.y * s1 + x2.y * c1);
-        }
-      }
     }
   }
 
@@ -450,8 +402,7 @@ int paged_attention_mma_prepare() {
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int window, int* err_flag, const float* rope_inv_freq,
-                        int fresh) {
+                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh) {
   int rc = paged_attention_mma_prepare();
   if (rc) return rc;
   CUtensorMap tm_k, tm_v;
@@ -478,20 +429,17 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
   if (nw == 8) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<8>, grid, dim3(256), mma_attn_smem(8), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
     return HB_OK;
   }
   if (nw == 2) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
   } else {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<4>, grid, dim3(128), mma_attn_smem(4), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, rope_inv_freq,
-                             (__nv_bfloat16*)const_cast<void*>(k_cache), (__nv_bfloat16*)const_cast<void*>(v_cache), fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
   }
   return HB_OK;
 }

@@ -33,7 +33,6 @@
 namespace hb {
 
 constexpr int kArThreads = 512;
-constexpr uint32_t kFlagSpin = 1u << 22;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -44,8 +43,8 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Wait until *p >= target (flags only grow). false when the limit ran out.
-__device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target) {
-  for (uint32_t it = 0; it < kFlagSpin; ++it) {
+__device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
     if (it > 64) __nanosleep(40);
   }
@@ -60,6 +59,7 @@ struct ArParams {
   int64_t total_vecs;   // 16-byte vectors in the message
   int64_t slice_vecs;   // two-shot: vectors per rank slice (one-shot: == total_vecs)
   int64_t vecs_per_cta; // sub-range of a slice handled by one CTA
+  uint32_t spin;        // polls before a wait gives up
 };
 
 template <typename T>
@@ -87,7 +87,7 @@ all_reduce_kernel(const ArParams p) {
 
   // A. every peer must have finished consuming the previous collective's data
   bool ok = true;
-  if (tid < R && tid != me) ok = wait_ge(&fl->done[tid], seq);
+  if (tid < R && tid != me) ok = wait_ge(&fl->done[tid], seq, p.spin);
   bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
 
   const int64_t v0 = (int64_t)b * p.vecs_per_cta;
@@ -116,7 +116,7 @@ all_reduce_kernel(const ArParams p) {
     __syncthreads();
     if (tid < R && tid != me) st_release_sys(&peer_flags(tid)->arrive1[b][me], target);
     ok = true;
-    if (tid < R && tid != me) ok = wait_ge(&fl->arrive1[b][tid], target);
+    if (tid < R && tid != me) ok = wait_ge(&fl->arrive1[b][tid], target, p.spin);
     all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
 
@@ -149,7 +149,7 @@ all_reduce_kernel(const ArParams p) {
       __syncthreads();
       if (tid < R && tid != me) st_release_sys(&peer_flags(tid)->arrive2[b][me], target);
       ok = true;
-      if (tid < R && tid != me) ok = wait_ge(&fl->arrive2[b][tid], target);
+      if (tid < R && tid != me) ok = wait_ge(&fl->arrive2[b][tid], target, p.spin);
       all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
       if (all_ok) {
         // D. gather the other ranks' reduced slices
@@ -218,6 +218,7 @@ int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_d
   if (count == 0) return fail(HB_ERR_EMPTY, "all_reduce: shard is empty");
   if (!buf) return fail(HB_ERR_INVALID_ARG, "all_reduce: null buffer");
   if (w->ws == 1) return HB_OK;  // single shard is a passthrough (src/parallel/comm.rs:50)
+  HB_CUDA_CHECK(cudaSetDevice(w->device));
   if (algo == HB_ALGO_NCCL) {
     NcclApi* api = nccl_api();
     if (!w->nccl || !api->ok) return fail(HB_ERR_NCCL, "all_reduce: NCCL communicator not initialised");
@@ -241,6 +242,7 @@ int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_d
   p.ws = R;
   p.rank = w->rank;
   p.two_shot = two ? 1 : 0;
+  p.spin = w->wait_limit;
   p.total_vecs = (int64_t)(bytes / 16);
   p.slice_vecs = two ? (p.total_vecs + R - 1) / R : p.total_vecs;
   const size_t need = (size_t)p.slice_vecs * 16 * (two ? 2 * R : R);
@@ -297,10 +299,13 @@ int hb_world_create_local(int n, const int* device_ids, size_t staging_bytes,
   HB_CHECK_ARG(worlds_out, "hb_world_create_local: null output");
   HB_CHECK_ARG(n >= 1 && n <= HB_MAX_RANKS, "tensor_parallel_size=%d outside [1, %d]", n, HB_MAX_RANKS);
   const int ndev = hb_device_count();
-  if (n > 1 && ndev < n)
+  // Without an explicit device list rank i runs on device i and n devices must exist
+  // (world.rs:108-114).  An explicit list may name a device more than once (ranks that share
+  // a GPU: useful for exercising the protocol, not for speed).
+  if (n > 1 && !device_ids && ndev < n)
     return hb::fail(HB_ERR_CUDA,
                     "tensor_parallel_size=%d requested but only %d CUDA device(s) detected. "
-                    "Use tensor_parallel_size 1 for single-GPU.", n, ndev);  // world.rs:108-114
+                    "Use tensor_parallel_size 1 for single-GPU.", n, ndev);
   std::vector<hb_world*> ws(n, nullptr);
   int rc = HB_OK;
   for (int i = 0; i < n && !rc; ++i) {
@@ -311,6 +316,7 @@ int hb_world_create_local(int n, const int* device_ids, size_t staging_bytes,
     cudaSetDevice(ws[i]->device);
     for (int j = 0; j < n && !rc; ++j) {
       if (i == j) continue;
+      if (ws[i]->device == ws[j]->device) { ws[i]->peer[j] = ws[j]->local; continue; }
       int can = 0;
       cudaDeviceCanAccessPeer(&can, ws[i]->device, ws[j]->device);
       if (!can) { rc = hb::fail(HB_ERR_CUDA, "device %d cannot access device %d", ws[i]->device, ws[j]->device); break; }
@@ -438,8 +444,24 @@ int hb_world_status(hb_world* w) {
   hb::CommFlags* fl = (hb::CommFlags*)w->local;
   HB_CUDA_CHECK(cudaMemcpy(w->host_status, &fl->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
   const int s = *w->host_status;
-  if (s) hb::set_error("a bounded wait on a peer flag ran out (status %d)", s);
+  if (s) {
+    // reading the status clears it: the next collective reports for itself
+    HB_CUDA_CHECK(cudaMemset(&fl->status, 0, sizeof(int32_t)));
+    hb::set_error("a bounded wait on a peer flag ran out (status %d)", s);
+  }
   return s;
+}
+
+int hb_world_set_wait_limit(hb_world* w, uint32_t polls) {
+  HB_CHECK_ARG(w, "hb_world_set_wait_limit: null world");
+  w->wait_limit = polls ? polls : (1u << 22);
+  return HB_OK;
+}
+
+int hb_world_set_early_trigger(hb_world* w, int on) {
+  HB_CHECK_ARG(w, "hb_world_set_early_trigger: null world");
+  w->trigger_early = on != 0;
+  return HB_OK;
 }
 
 int hb_all_reduce(hb_world* w, void* stream, void* buf, size_t count, hb_dtype dtype,

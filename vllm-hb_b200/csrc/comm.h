@@ -12,6 +12,7 @@ namespace hb {
 constexpr int kMaxCommCtas = 128;
 constexpr size_t kFlagBytes = 64 * 1024;
 constexpr int kMaxFusedTiles = 256;  // N <= 32768 in the fused row-parallel kernel
+constexpr int kMaxPushFlags = 4096;  // row blocks x ranks x tiles per slice of one pushed projection
 
 struct CommFlags {
   // written by peers (release, system scope), polled locally
@@ -20,6 +21,8 @@ struct CommFlags {
   uint32_t arrive2[kMaxCommCtas][HB_MAX_RANKS];     // per-CTA: reduced slice pushed
   uint32_t pflag[kMaxFusedTiles * HB_MAX_RANKS];    // fused kernel: partial of tile t from rank p landed
   uint32_t gflag[kMaxFusedTiles];                   // fused kernel: reduced tile t (+ row sums) landed
+  uint32_t sflag[kMaxFusedTiles * HB_MAX_RANKS];    // exchange + norm kernel: reduced slice of row t from rank p landed
+  uint32_t tflag[kMaxPushFlags];                    // GEMM push epilogue: tile of a slice for a row block landed
   // local only
   uint32_t seq;        // collectives completed on this rank
   uint32_t finished;   // CTAs of the running kernel that are done
@@ -40,6 +43,8 @@ struct hb_world {
   bool owns_local = true;
   bool attached = false;
   void* nccl = nullptr;               // ncclComm_t when hb_world_init_nccl ran
+  uint32_t wait_limit = 1u << 22;     // polls before a device-side wait on a peer flag gives up
+  bool trigger_early = false;         // exchange kernels let their successor become resident while they wait
   int32_t* host_status = nullptr;     // pinned mirror for hb_world_status
 };
 
@@ -51,8 +56,18 @@ int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_d
 // All-reduce of `partial` + residual add + RMSNorm in one kernel (ar_norm.cu); the values
 // of world_all_reduce followed by hb_add_rms_norm.
 bool ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
+// How a GEMM epilogue pushed its partial into the reducers' staging (gemm_tc.cu, kEpiPush):
+// tiles of 128 features x row_block batch rows; every rank's column slice is
+// tiles_per_slice tiles wide.
+struct PushGeometry {
+  int row_block = 0;
+  int tiles_per_slice = 0;
+};
+// True when a [M, N] row-parallel projection on this world can leave through the push epilogue.
+bool push_exchange_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
+// staged != null: `partial` is ignored, the slices were pushed by the GEMM (two-shot form).
 int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
                       const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
-                      hb_dtype dtype, hb_algo algo);
+                      hb_dtype dtype, hb_algo algo, const PushGeometry* staged = nullptr);
 
 }  // namespace hb

@@ -60,6 +60,8 @@ struct StepPlans {
   int attn_splits = 1;
   bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
   bool rope_epi = false;    // RoPE + KV write folded into the q|k|v GEMM epilogue (TcNormLink)
+  bool push = false;        // o_proj / down_proj epilogues push their partials to the reducing ranks (kEpiPush)
+  PushGeometry geo_o, geo_down;
   int64_t launches = 0;  // kernels in one step (fixed per batch size)
   cudaGraphExec_t graph = nullptr;
 };
@@ -114,9 +116,7 @@ struct hb_engine {
   void* d_gemm_ws = nullptr;
   size_t gemm_ws_bytes = 0;
   int* d_err = nullptr;
-  bool use_tc = false, use_graph = true, fused_swiglu = true, use_fused = false;
-  bool fuse_rope = false;  // RoPE + KV append inside the tensor-core attention kernel
-  void* d_fused_ws = nullptr;
+  bool use_tc = false, use_graph = true, fused_swiglu = true;
   std::map<int, hb::StepPlans> plans;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = -1.f;
@@ -347,32 +347,8 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = dev_alloc(e, (void**)&e->d_inv_freq, inv.size() * 4))) return rc;
   HB_CUDA_CHECK(cudaMemcpy(e->d_inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
   if ((rc = paged_attention_mma_prepare())) return rc;
-  {
-    // Off by default: measured inside the step's CUDA graph, the rotation and the append at
-    // the head of every attention CTA delay its first KV loads by more than the separate
-    // 6 us kernel costs (4.78 against 4.74 ms per step on the 8B shape).  HB_FUSE_ROPE=1 enables it.
-    const char* fr = getenv("HB_FUSE_ROPE");
-    e->fuse_rope = fr && fr[0] == '1' && !getenv("HB_ATTN") &&
-                   paged_attention_mma_supported(e->d_qkv, e->qkv_rows, e->kc[0], e->vc[0], (int)(e->hq_l / e->hkv_l),
-                                                 (int)e->hd, e->num_blocks, (int)e->hkv_l, e->dtype);
-  }
   e->attn_ws_bytes = hb_attention_workspace_bytes(B, (int)e->hq_l, (int)e->hd, 16);
   if ((rc = dev_alloc(e, &e->d_attn_ws, e->attn_ws_bytes))) return rc;
-  // The row-parallel projections run as GEMM -> peer-memory all-reduce -> add+norm by
-  // default: measured at 1 and 2 ranks that sequence is still ahead of the one-kernel
-  // fused form (whose grid-wide wait costs more than the two kernel boundaries it
-  // saves).  HB_FUSED=1 selects the fused kernel.
-  const char* ff = getenv("HB_FUSED");
-  e->use_fused = e->use_tc && ff && ff[0] == '1';
-  if (e->use_fused) {
-    const size_t fw = std::max(rowpar_fused_workspace_bytes(B, e->H, e->hq_l * e->hd),
-                               rowpar_fused_workspace_bytes(B, e->H, e->I_e));
-    if (fw == 0) e->use_fused = false;
-    else {
-      if ((rc = dev_alloc(e, &e->d_fused_ws, fw))) return rc;
-      HB_CUDA_CHECK(cudaMemset(e->d_fused_ws, 0, fw));
-    }
-  }
   return HB_OK;
 }
 
@@ -400,7 +376,7 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
     // Single rank: residual add and RMSNorm ride in the GEMM epilogues (HB_DEFER_NORM=0:
     // separate add+norm kernels) when o_proj and down_proj get cluster plans.
     static const bool no_defer = [] { const char* v = getenv("HB_DEFER_NORM"); return v && v[0] == '0'; }();
-    sp.defer_norm = e->ws == 1 && !e->use_fused && !no_defer && e->H % 128 == 0 && !e->moe;  // the router reads normalised x
+    sp.defer_norm = e->ws == 1 && !no_defer && e->H % 128 == 0 && !e->moe;  // the router reads normalised x
     if (sp.defer_norm) {
       TcGemmPlan probe_o, probe_d;
       auto& w0 = e->layers[0];
@@ -408,7 +384,27 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
       if ((rc = gemm_tc_plan(&probe_d, e->d_act, w0.wdown, B, e->H, e->I_e, kEpiResidual, false, e->device))) return rc;
       sp.defer_norm = probe_o.cluster && probe_d.cluster && probe_o.m_tiles == 1 && probe_d.m_tiles == 1;
     }
-    const int row_epi = sp.defer_norm ? kEpiResidual : kEpiStore;
+    // Several ranks: the row-parallel GEMMs push their partial tiles straight into the
+    // reducing ranks' staging (the first hop of the all-reduce rides in the GEMM epilogue)
+    // when the batch is large enough for the two-hop exchange (HB_PUSH=0: GEMM, then the
+    // exchange kernel reads the partial back; HB_PUSH=1: push at every batch size).
+    {
+      const char* pe = getenv("HB_PUSH");
+      const bool off = pe && pe[0] == '0', always = pe && pe[0] == '1';
+      const bool two_hop = e->ws > 2 && (size_t)B * e->H * e->es > 128 * 1024;
+      sp.push = e->ws > 1 && !off && (always || two_hop) && push_exchange_supported(e->world, B, e->H, e->dtype);
+      if (sp.push) {
+        TcGemmPlan probe_o, probe_d;
+        auto& w0 = e->layers[0];
+        if ((rc = gemm_tc_plan(&probe_o, e->d_attn, w0.wo, B, e->H, e->hq_l * e->hd, kEpiPush, false, e->device))) return rc;
+        if ((rc = gemm_tc_plan(&probe_d, e->d_act, w0.wdown, B, e->H, e->I_e, kEpiPush, false, e->device))) return rc;
+        sp.push = probe_o.cluster && probe_d.cluster && probe_o.m_tiles == 1 && probe_d.m_tiles == 1;
+        const int tiles = (int)(e->H / 128 / e->ws);
+        sp.geo_o = {probe_o.m_pad / probe_o.splits, tiles};
+        sp.geo_down = {probe_d.m_pad / probe_d.splits, tiles};
+      }
+    }
+    const int row_epi = sp.defer_norm ? kEpiResidual : (sp.push ? kEpiPush : kEpiStore);
     for (int64_t l = 0; l < e->L; ++l) {
       auto& w = e->layers[l];
       if ((rc = gemm_tc_plan(&sp.layer[l * 4 + kQkv], e->d_x, w.wqkv, B, e->qkv_rows, e->H, kEpiStore, false, e->device))) return rc;
@@ -422,12 +418,28 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
       for (int k = 0; k < 4; ++k) ws = std::max(ws, sp.layer[l * 4 + k].workspace_bytes());
     }
     if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
+    if (e->ws > 1) {
+      // The GEMMs that follow an exchange (q|k|v after down_proj's, gate|up after o_proj's) may
+      // become resident while the exchange waits for its peers and HBM is idle: they then
+      // request this many MB of their weights into L2 ahead of their dependency wait.
+      static const int mb = [] { const char* v = getenv("HB_XCHG_PREFETCH_MB"); return v ? atoi(v) : 0; }();
+      if (mb > 0) {
+        hb_world_set_early_trigger(e->world, 1);
+        for (int64_t l = 0; l < e->L; ++l)
+          for (int kind : {(int)kQkv, (int)kGateUp}) {
+            TcGemmPlan& pl = sp.layer[l * 4 + kind];
+            const size_t ctas = (size_t)pl.n_tiles * pl.m_tiles * pl.splits;
+            const size_t chunk = (size_t)128 * 64 * 2 * (pl.epilogue == kEpiSwiGLU ? 2 : 1);
+            pl.l2_burst = (int)(((size_t)mb << 20) / (ctas * chunk));
+          }
+      }
+    }
     ws = std::max(ws, sp.lm_head.workspace_bytes());
     // RoPE and the KV write ride in the q|k|v GEMM epilogue when its output tile is one head
     // (HB_ROPE_EPI=0: the separate kernel)
     const char* re_env = getenv("HB_ROPE_EPI");  // read per plan, so that tests can compare both forms
     const bool no_rope_epi = re_env && re_env[0] == '0';
-    sp.rope_epi = !no_rope_epi && !e->fuse_rope && e->dtype == HB_BF16 && e->hd == 128 && e->L > 0 &&
+    sp.rope_epi = !no_rope_epi && e->dtype == HB_BF16 && e->hd == 128 && e->L > 0 &&
                   gemm_tc_rope_epilogue_ok(sp.layer[kQkv]);
     if (sp.defer_norm) {
       auto can_scale = [](const TcGemmPlan& pl) { return pl.tma_store && (pl.cluster || pl.splits == 1) && pl.m_tiles == 1; };
@@ -545,6 +557,13 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
   const char* ae_env = getenv("HB_ATTN_EARLY");
   const int attn_fresh = (ae_env && ae_env[0] == '0') ? -1 : B;
   const bool rope_epi = e->use_tc && sp->rope_epi;
+  TcNormLink push_link;
+  if (sp->push) {
+    push_link.push_peers = e->world->peer;
+    push_link.push_ranks = e->ws;
+    push_link.push_rank = e->rank;
+    push_link.push_spin = e->world->wait_limit;
+  }
   if (rope_epi) {
     // the step's (cos, sin) table, shared by the q|k|v epilogues of every layer
     prof_mark(e, kCatRopeKv);
@@ -570,7 +589,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = run_gemm(e, sp, l, kQkv, e->d_qkv, e->d_x, w.wqkv, B, e->qkv_rows, e->H, false,
                        ((defer && l > 0) || rope_epi) ? &qkv_link : nullptr))) return rc;
     // RoPE + KV append                                        llama_tp.rs:242-259
-    if (!e->fuse_rope && !rope_epi) {
+    if (!rope_epi) {
       prof_mark(e, kCatRopeKv);
       if ((rc = rope_kv_write(st, e->d_qkv, e->kc[l], e->vc[l], d_pos, d_slots, e->d_inv_freq, B,
                               (int)e->hq_l, (int)e->hkv_l, (int)e->hd, e->num_blocks, e->dtype))) return rc;
@@ -581,15 +600,17 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype, e->d_err, (int)e->window, e->fuse_rope ? e->d_inv_freq : nullptr,
-                              attn_fresh))) return rc;
+                              e->dtype, e->d_err, (int)e->window, attn_fresh))) return rc;
     e->last_launches += 1 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);
-    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->hq_l * e->hd)) {
-      // one kernel: GEMM tiles -> peer staging -> reduce + residual -> row scales -> norm
-      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_attn, w.wo, e->d_h, w.norm_post, B, e->H,
-                             e->hq_l * e->hd, eps, HB_ALGO_AUTO, e->d_fused_ws))) return rc;
+    if (sp->push) {
+      // the GEMM epilogue pushes each tile to the rank that reduces its column slice; the
+      // exchange kernel starts at the wait                      llama_tp.rs:327,533-552
+      if ((rc = run_gemm(e, sp, l, kO, nullptr, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false, &push_link))) return rc;
+      prof_mark(e, kCatComm);
+      if ((rc = world_ar_add_norm(e->world, st, e->d_x, e->d_h, nullptr, e->d_h, w.norm_post, B, e->H, eps, e->dtype,
+                                  HB_ALGO_TWO_SHOT, &sp->geo_o))) return rc;
       ++e->last_launches;
     } else if (defer) {
       // h += o_proj(attn); x' = h * w_post; row sums for the gate|up GEMM
@@ -640,9 +661,11 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     // residual + the next layer's input norm (or the final norm)   llama_tp.rs:566-571,517-522,349-351
     const void* nw = (l + 1 < e->L) ? e->layers[l + 1].norm_in : e->final_norm;
     prof_mark(e, kCatGemmDown);
-    if (e->use_fused && rowpar_fused_supported(e->world, B, e->H, e->I_e)) {
-      if ((rc = rowpar_fused(e->world, st, e->d_x, e->d_h, e->d_act, w.wdown, e->d_h, nw, B, e->H, e->I_e, eps,
-                             HB_ALGO_AUTO, e->d_fused_ws))) return rc;
+    if (sp->push) {
+      if ((rc = run_gemm(e, sp, l, kDown, nullptr, e->d_act, w.wdown, B, e->H, e->I_e, false, &push_link))) return rc;
+      prof_mark(e, kCatComm);
+      if ((rc = world_ar_add_norm(e->world, st, e->d_x, e->d_h, nullptr, e->d_h, nw, B, e->H, eps, e->dtype,
+                                  HB_ALGO_TWO_SHOT, &sp->geo_down))) return rc;
       ++e->last_launches;
     } else if (defer) {
       TcNormLink produce;
@@ -967,9 +990,17 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
     const hb::StTensor* s = it->second;
     if (s->dtype != "F32" && s->dtype != "F16" && s->dtype != "BF16")
       return hb::fail(HB_ERR_UNSUPPORTED_DTYPE, "%s has dtype %s", name.c_str(), s->dtype.c_str());
-    if (s->numel() != rows * cols)
-      return hb::fail(HB_ERR_IO, "%s has %lld elements, expected %lld x %lld", name.c_str(),
+    // the shape itself, not only the element count: a transposed matrix must not be sharded
+    const bool shape_ok = rows == 1 ? ((s->shape.size() == 1 && s->shape[0] == cols) ||
+                                       (s->shape.size() == 2 && s->shape[0] == 1 && s->shape[1] == cols))
+                                    : (s->shape.size() == 2 && s->shape[0] == rows && s->shape[1] == cols);
+    if (!shape_ok)
+      return hb::fail(HB_ERR_IO, "%s has %lld elements in a shape other than the expected [%lld, %lld]", name.c_str(),
                       (long long)s->numel(), (long long)rows, (long long)cols);
+    const size_t src_es = s->dtype == "F32" ? 4 : 2;
+    if (s->nbytes != (size_t)(rows * cols) * src_es)
+      return hb::fail(HB_ERR_IO, "%s holds %zu bytes, [%lld, %lld] of %s needs %zu", name.c_str(), s->nbytes,
+                      (long long)rows, (long long)cols, s->dtype.c_str(), (size_t)(rows * cols) * src_es);
     *t = s;
     return HB_OK;
   };
@@ -1138,16 +1169,7 @@ int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t se
                     seq_pos, (long long)s->len);
   // Prefill runs through the decode kernels in chunks whose rows are consecutive positions
   // of this sequence: causal attention over the growing cache equals the masked prefill of
-  // llama_tp.rs:313-316.  (The optional in-attention RoPE appends one token per CTA, which a
-  // chunk cannot use: token by token then.)
-  if (e->fuse_rope) {
-    for (size_t i = 0; i < n; ++i) {
-      hb_seq* one[1] = {s};
-      int rc = hb::decode_step(e, one, 1, ids + i, nullptr, i + 1 == n ? logits_out : nullptr);
-      if (rc) return rc;
-    }
-    return HB_OK;
-  }
+  // llama_tp.rs:313-316.
   {
     int rc = hb::prefill(e, s, ids, n, logits_out);
     if (rc) return rc;

@@ -16,6 +16,7 @@ enum TcEpilogue : int {
   kEpiStore = 0,     // Y = acc (bf16, or f32 when out_f32)
   kEpiSwiGLU = 1,    // W rows are [gate tile | up tile] pairs: Y = silu(gate) * up, N_out = N/2
   kEpiResidual = 2,  // deferred RMSNorm producer (cluster plans only), see TcNormLink
+  kEpiPush = 3,      // row-parallel partial pushed into the reducing ranks' staging, see TcNormLink
 };
 
 // Deferred RMSNorm between two GEMMs of a single-rank decode step.  Instead of a separate
@@ -54,6 +55,17 @@ struct TcNormLink {
   void* v_cache = nullptr;
   int n_q_heads = 0, n_kv_heads = 0;
   int64_t num_blocks = 0;
+  // kEpiPush (cluster plans, bf16): the first hop of the all-reduce that follows a
+  // row-parallel projection happens here.  Rank q of push_ranks reduces the q-th column slice
+  // of the [M, N] result; a CTA that has staged its [rows][128] tile writes it with 16-byte
+  // stores straight into rank q's staging (peer memory over NVLink, or this rank's own) and
+  // raises the tile's arrival flag there with a system-scope release.  Nothing is written to
+  // Y.  The consumer is world_ar_add_norm(..., staged) in ar_norm.cu.  push_peers are the
+  // staging bases of all ranks (hb_world::peer), push_spin the poll limit of the one wait
+  // (peers done with the previous exchange).
+  void* const* push_peers = nullptr;
+  int push_ranks = 0, push_rank = 0;
+  uint32_t push_spin = 0;
 };
 
 // A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by
@@ -67,9 +79,12 @@ struct TcGemmPlan {
   int n_tiles = 0;    // ceil(N / 128)
   int splits = 1;     // split-K factor
   bool cluster = false;  // the splits of a tile form a thread-block cluster (on-chip reduction)
-  bool bulk = false;     // cluster exchange by bulk copies into a dedicated receive area
   int stages = 0;
   int tmem_cols = 0;
+  // k-chunks per CTA requested into L2 before the dependency wait, after the ones that fill
+  // the shared-memory pipeline.  Set by the caller for a GEMM that follows a kernel during
+  // which HBM is idle; measured harmful (-2 % to -7 % per step) after HBM-bound kernels.
+  int l2_burst = 0;
   size_t smem_bytes = 0;
   int epilogue = kEpiStore;
   bool out_f32 = false;

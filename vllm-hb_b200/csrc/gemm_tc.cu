@@ -32,8 +32,10 @@
 #include <cstring>
 #include <mutex>
 
+#include "comm.h"
 #include "common.h"
 #include "gemm.h"
+#include "peer_sync.cuh"
 #include "tc_core.cuh"
 
 namespace hb {
@@ -47,8 +49,10 @@ struct TcParams {
   int64_t ldy;
   int up_row_offset;        // SwiGLU: first row of the up projection inside W
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
-  int bulk;                 // cluster exchange by bulk copies into a dedicated receive area
   int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
+  // k-chunks of this CTA's range requested into L2 before the dependency wait, beyond the
+  // ones that go straight to shared memory (see TcGemmPlan::l2_burst)
+  int l2_burst;
   // Deferred RMSNorm (see TcNormLink in gemm.h).  Producer (epilogue kEpiResidual, cluster
   // form only): h = resid + Y, written through tm_h; Y' = h * norm_w written through tm_y;
   // row sums of h^2 over this tile's 128 features to rowsq_out[row * rowsq_stride + tile].
@@ -70,6 +74,12 @@ struct TcParams {
   __nv_bfloat16* v_cache;
   int rope_nq, rope_nkv;
   int64_t kv_num_blocks;
+  // kEpiPush (see TcNormLink): staging bases of all ranks, this rank, tiles and 16-byte
+  // vectors per rank slice, poll limit
+  void* push_peer[HB_MAX_RANKS];
+  int push_R, push_me, push_T;
+  int64_t push_sv;
+  uint32_t push_spin;
   void* Y;
   float* partials;
   int* counters;
@@ -132,8 +142,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_last;
+  __shared__ uint32_t s_seq;
+  __shared__ int s_push_ok;
   __shared__ __align__(8) uint64_t s_resid;  // residual tile landed (kEpiResidual)
-  __shared__ __align__(8) uint64_t s_recv;   // partners' partials landed (bulk exchange)
   __shared__ float s_rscale[256];            // row scales of the deferred norm (consumer)
   __shared__ float s_pscale[256];            // row scales applied after the activation (MoE weights)
 
@@ -164,7 +175,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     mbar_init(smem_u32(&s_done), 1);
     mbar_init(smem_u32(&s_resid), 1);
-    mbar_init(smem_u32(&s_recv), 1);
     s_abort = 0;
     s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -181,13 +191,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
-  if (p.bulk) {
-    // partners complete bytes on this CTA's barrier: arm it, then make sure every CTA of the
-    // cluster has an initialised barrier before anyone can send
-    if (tid == 0)
-      mbar_expect_tx(smem_u32(&s_recv), (uint32_t)(p.splits - 1) * (uint32_t)(n_acc * (p.m_pad / p.splits) * kTileN * 4));
-    cluster_sync_all();
-  }
   TC_TRACE(tid == 0, 1);
   pdl_launch_dependents();  // the next kernel may start its own prologue / weight prefetch
   if (!(warp == 0 && lane == 0)) pdl_wait();  // the producer waits after its weight prefetch
@@ -214,6 +217,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       s_rscale[i] = sc;
     }
   }
+  if (warp == 3 && p.epilogue == kEpiPush) {
+    // push epilogue: while the weights stream, learn the number of the coming exchange and
+    // make sure every peer is done reading the staging of the previous one (the previous
+    // exchange kernel of this rank has completed: griddepcontrol.wait above)
+    CommFlags* fl = reinterpret_cast<CommFlags*>(p.push_peer[p.push_me]);
+    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(&fl->seq);
+    bool okp = true;
+    if (lane < p.push_R && lane != p.push_me) okp = peer_wait_ge(&fl->done[lane], seq, p.push_spin);
+    okp = __all_sync(0xffffffffu, okp);
+    if (lane == 0) {
+      s_seq = seq;
+      s_push_ok = okp ? 1 : 0;
+    }
+  }
   if (warp >= 2 && p.post_scale) {
     const int grp = (blockIdx.x / p.splits) / p.post_tiles_per_group;
     for (int i = tid - 64; i < p.m_pad; i += 64) {
@@ -225,6 +242,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       // ---------------------------------------------------------- TMA producer
       int armed = 0;  // k-chunks whose copies were issued
+      const uint64_t w_policy = l2_policy_evict_first();
+      // every weight byte is read once per launch: it may leave L2 first (measured +1 % on the
+      // 8B decode step against the default policy)
+      auto load_w = [&](uint32_t dst, int kx, int row, uint32_t bar) {
+        tma_load_2d_hint(dst, &tm_w, kx, row, bar, w_policy);
+      };
       // Weights never depend on the previous kernel: the first stages' weight slabs are
       // requested before waiting for it; activations only afterwards.
       const int pre = min(p.stages, n_kc);
@@ -233,8 +256,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t sa = smem_base + i * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
         const int kx = (kc0 + i) * kTileK;
-        tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
-        if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
+        load_w(sa, kx, tile * kTileN, full);
+        if (swiglu) load_w(sa + a_bytes, kx, p.up_row_offset + tile * kTileN, full);
+      }
+      // ... and (l2_burst > 0) the chunks after them are requested into L2: for a GEMM whose
+      // predecessor leaves HBM idle (an exchange over NVLink).
+      for (int i = pre; i < min(n_kc, pre + p.l2_burst); ++i) {
+        const int kx = (kc0 + i) * kTileK;
+        tma_prefetch_2d(&tm_w, kx, tile * kTileN);
+        if (swiglu) tma_prefetch_2d(&tm_w, kx, p.up_row_offset + tile * kTileN);
       }
       pdl_wait();
       TC_LAUNCH_TRACE(3);
@@ -251,8 +281,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t sa = smem_base + s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
         const int kx = (kc0 + i) * kTileK;
-        tma_load_2d(sa, &tm_w, kx, tile * kTileN, full);
-        if (swiglu) tma_load_2d(sa + a_bytes, &tm_w, kx, p.up_row_offset + tile * kTileN, full);
+        load_w(sa, kx, tile * kTileN, full);
+        if (swiglu) load_w(sa + a_bytes, kx, p.up_row_offset + tile * kTileN, full);
         tma_load_2d(sa + a_bytes * n_acc, &tm_x, kx, m_tile * p.m_pad, full);
         armed = i + 1;
       }
@@ -331,11 +361,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // partials in split order (deterministic) and runs the epilogue for its rows.
     // Both cluster barriers are reached unconditionally.
     const int S = p.splits, CW = p.m_pad / S;          // CW is a multiple of 4
-    // receive area [S-1][n_acc][CW/4][128 features][4 columns]: over the idle pipeline buffers,
-    // or (bulk exchange) a dedicated area behind them so that partners need not wait for
-    // this CTA's pipeline to drain
-    const uint32_t recv_byte_off = p.bulk ? (uint32_t)p.stages * stage_bytes : 0u;
-    float* recv = reinterpret_cast<float*>(smem_gen + recv_byte_off);
+    // receive area [S-1][n_acc][CW/4][128 features][4 columns] over the idle pipeline buffers
+    float* recv = reinterpret_cast<float*>(smem_gen);
     const int slot_floats = n_acc * CW * kTileN;
     const uint32_t out_off = (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
     const bool residual = p.epilogue == kEpiResidual;
@@ -349,48 +376,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_expect_tx(bar, tile_b);
       tma_load_2d(smem_base + resid_off, &tm_h, tile * kTileN, m_base + split * CW, bar);
     }
-    if (!p.bulk) cluster_sync_all();  // every partner's pipeline buffers are idle from here on
+    cluster_sync_all();  // every partner's pipeline buffers are idle from here on
     TC_TRACE(tid == 0, 5);
-    if (ok_all && p.bulk) {
-      // stage the columns of every other owner in this CTA's own (idle) pipeline buffers,
-      // then one bulk copy per partner moves them into its receive area
-      for (int acc = 0; acc < n_acc; ++acc) {
-        for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
-          if (c0 / CW == split && (c0 + 15) / CW == split) continue;
-          float v[16];
-          tmem_ld16(t_lane + acc * p.m_pad + c0, v);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = c0 + 4 * q, owner = c / CW;
-            if (owner != split) {
-              const int o_idx = owner < split ? owner : owner - 1;
-              float4* dst = reinterpret_cast<float4*>(smem_gen) +
-                            (o_idx * slot_floats / 4 + (acc * (CW >> 2) + ((c % CW) >> 2)) * kTileN + row);
-              *dst = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            }
-          }
-        }
-      }
-      fence_async_smem();
-    }
-    if (p.bulk) {
-      __syncthreads();
-      if (ok_all && tid == 0) {
-        const uint32_t slot_bytes = (uint32_t)slot_floats * 4u;
-        for (int owner = 0; owner < S; ++owner) {
-          if (owner == split) continue;
-          const int o_idx = owner < split ? owner : owner - 1;
-          const int my_slot = split < owner ? split : split - 1;
-          bulk_copy_to_partner(cluster_map(smem_base + recv_byte_off + (uint32_t)my_slot * slot_bytes, (uint32_t)owner),
-                               smem_base + (uint32_t)o_idx * slot_bytes, slot_bytes,
-                               cluster_map(smem_u32(&s_recv), (uint32_t)owner));
-        }
-        // and wait for the S-1 partials addressed to this CTA
-        if (!mbar_wait(smem_u32(&s_recv), 0, &s_abort)) s_abort = 1;
-      }
-      __syncthreads();
-    }
-    if (ok_all && !p.bulk) {
+    if (ok_all) {
       for (int acc = 0; acc < n_acc; ++acc) {
         for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
           // groups this CTA owns entirely stay in tensor memory (uniform over the CTA)
@@ -412,9 +400,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
       }
     }
-    if (!p.bulk) cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
+    cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
     TC_TRACE(tid == 0, 6);
-    bool resid_ok = !(p.bulk && s_abort);
+    bool resid_ok = true;
     const float w_norm = (residual && n_glob < p.N) ? __bfloat162float(p.norm_w[n_glob]) : 0.f;
     if (ok_all) {
       const int c_lo = split * CW;
@@ -556,6 +544,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
       }
     }
+    if (p.epilogue == kEpiPush) {
+      // ---- first hop of the all-reduce: the staged bf16 tile goes to the rank that reduces
+      // this tile's column slice (16-byte stores into its staging over NVLink, or into this
+      // rank's own), then the tile's arrival flag is raised there
+      store_y = false;
+      const int R = p.push_R, me = p.push_me, T = p.push_T;
+      const int q = tile / T, ti = tile % T;
+      CommFlags* fl = reinterpret_cast<CommFlags*>(p.push_peer[me]);
+      // s_seq / s_push_ok were written by warp 3 before the epilogue's first CTA barrier
+      const uint32_t seq = s_seq;
+      const bool go = tail_ok && s_push_ok != 0;
+      if (go) {
+        const int row0 = m_base + split * CW;
+        uint4* dst = reinterpret_cast<uint4*>((uint8_t*)p.push_peer[q] + kFlagBytes) +
+                     ((int64_t)me * p.M + row0) * p.push_sv + ti * 16;
+        const uint4* src = reinterpret_cast<const uint4*>(smem_gen + out_off);
+        for (int idx = tid; idx < CW * 16; idx += kTcThreads) {
+          const int rr = idx >> 4, vv = idx & 15;
+          if (row0 + rr < p.M) dst[(int64_t)rr * p.push_sv + vv] = src[idx];
+        }
+        __syncthreads();  // orders every thread's stores before the release below
+        if (tid == 0)
+          peer_st_release(&reinterpret_cast<CommFlags*>(p.push_peer[q])->tflag[((row0 / CW) * R + me) * T + ti],
+                          seq + 1);
+      } else if (tid == 0 && tail_ok) {
+        atomicExch(&fl->status, HB_ERR_TIMEOUT);
+        if (p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
+      }
+    }
     if (tail_ok && store_y && tid == 0 && m_base + split * CW < p.M) {
       tma_store_2d(&tm_y, smem_base + out_off, tile * kTileN, m_base + split * CW);
       if (residual) tma_store_2d(&tm_h, smem_base + h_off, tile * kTileN, m_base + split * CW);
@@ -563,9 +580,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       tma_store_wait_read();
     }
     if (!tail_ok && ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
-    // bulk exchange: a partner's copy engine may still be reading this CTA's staging until
-    // that partner has seen all its bytes; nobody leaves before everybody has
-    if (p.bulk) cluster_sync_all();
     TC_TRACE(tid == 0, 12);
     if (!ok_all && tid == 0 && p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
   } else if (ok_all && p.splits == 1 && p.tma_store) {
@@ -781,16 +795,9 @@ static int pick_splits(int units, int k_chunks, int slots) {
 // shared memory).  One SM draws at most ~34 GB/s of weights from HBM (measured), so
 // every GEMM wants at least one CTA on each SM: the smallest power of two that
 // covers the SMs, at most 8 (portable cluster size), each CTA keeping >= 4 K chunks.
-// HB_TC_BULK=1 selects the bulk-copy exchange (see TcParams::bulk); the default is the
-// 16-byte remote-store exchange.
-static bool bulk_exchange_enabled() {
-  const char* e = getenv("HB_TC_BULK");
-  return e && e[0] == '1';
-}
-
 static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
-  int s = 1, cap = 8;
-  if (const char* ev = getenv("HB_TC_MAX_SPLITS")) cap = std::max(1, atoi(ev));  // experiment knob
+  int s = 1;
+  const int cap = 8;  // portable cluster size
   while (s < cap && units * s < sm_count && k_chunks / (s * 2) >= 4) s *= 2;
   return s;
 }
@@ -826,8 +833,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const size_t stage = (size_t)kTileN * kTileK * 2 * n_acc + (size_t)pl.m_pad * kTileK * 2;
   // two CTAs per SM when the stages allow it, so one CTA's epilogue hides under the
   // other's loads
-  size_t budget = 110 * 1024;
-  if (const char* ev = getenv("HB_TC_SMEM_KB")) budget = (size_t)atoi(ev) * 1024;  // experiment knob
+  const size_t budget = 110 * 1024;
   pl.stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, budget / stage));
   pl.smem_bytes = pl.stages * stage + 1024;
   if (pl.smem_bytes > di.smem_optin)
@@ -862,7 +868,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
       const int small_stages = pl.stages;
       const size_t big = 200 * 1024;
       const int big_stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, big / stage));
-      const bool big_ok = !getenv("HB_TC_SMEM_KB") && big_stages > small_stages &&
+      const bool big_ok = big_stages > small_stages &&
                           (size_t)big_stages * stage + 1024 <= di.smem_optin;
       while (pl.splits > 1) {
         if (pl.m_pad / pl.splits >= 4 && pl.m_pad % (4 * pl.splits) == 0) {
@@ -882,25 +888,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
                  pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
-  // Bulk exchange: the partners' partials land in a dedicated area behind the pipeline
-  // buffers (no barrier before sending), moved by one bulk copy per partner.  Taken when
-  // pipeline + receive area still fit the shared-memory budget of the plan.
-  pl.bulk = false;
-  if (pl.cluster && bulk_exchange_enabled()) {
-    const size_t cw = (size_t)pl.m_pad / pl.splits;
-    const size_t recv_bytes = (size_t)(pl.splits - 1) * n_acc * cw * kTileN * sizeof(float);
-    const size_t cap = pl.smem_bytes > 120 * 1024 ? (size_t)224 * 1024 : (size_t)113 * 1024;  // keep the CTAs-per-SM class
-    int st = pl.stages;
-    while (st > 2 && (size_t)st * stage + recv_bytes + 1024 > cap) --st;
-    const int keep = pl.stages;
-    pl.stages = st;
-    if ((size_t)st * stage + recv_bytes + 1024 <= cap && recv_fits(pl.splits)) {
-      pl.bulk = true;
-      pl.smem_bytes = (size_t)st * stage + recv_bytes + 1024;
-    } else {
-      pl.stages = keep;
-    }
-  }
+  pl.l2_burst = 0;
   const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
@@ -958,15 +946,30 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
   p.cluster = pl.cluster ? 1 : 0;
-  p.bulk = pl.bulk ? 1 : 0;
+  p.l2_burst = pl.l2_burst;
   CUtensorMap tm_y;
   memset(&tm_y, 0, sizeof(tm_y));
   const size_t y_elt = pl.out_f32 ? 4 : 2;
-  const bool y_ok = (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && ((size_t)ldy * y_elt) % 16 == 0;
+  const bool push = pl.epilogue == kEpiPush;
+  const bool y_ok = push || ((reinterpret_cast<uintptr_t>(Y) & 15) == 0 && ((size_t)ldy * y_elt) % 16 == 0);
   if (pl.cluster && !y_ok)
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: output must be 16-byte aligned with rows of a multiple of 16 bytes");
   p.tma_store = (pl.tma_store && y_ok && (pl.cluster || pl.splits == 1)) ? 1 : 0;
-  if (p.tma_store) {
+  if (push) {
+    const int R = link ? link->push_ranks : 0;
+    if (!pl.cluster || pl.m_tiles != 1 || pl.out_f32 || !link || !link->push_peers || R < 2 || R > HB_MAX_RANKS ||
+        link->push_rank < 0 || link->push_rank >= R || pl.N % ((int64_t)R * kTileN) ||
+        pl.m_pad / pl.splits < 1 ||
+        (int64_t)((pl.M + pl.m_pad / pl.splits - 1) / (pl.m_pad / pl.splits)) * (pl.N / kTileN) > kMaxPushFlags)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the push epilogue needs a cluster plan, bf16 output and rank slices of whole tiles");
+    for (int q = 0; q < R; ++q) p.push_peer[q] = link->push_peers[q];
+    p.push_R = R;
+    p.push_me = link->push_rank;
+    p.push_T = (int)(pl.N / kTileN / R);
+    p.push_sv = (int64_t)p.push_T * 16;
+    p.push_spin = link->push_spin ? link->push_spin : (1u << 22);
+  }
+  if (p.tma_store && !push) {
     const int box_rows = pl.cluster ? pl.m_pad / pl.splits : 16;
     int rc = encode_out_map(&tm_y, Y, pl.M, pl.N, ldy, pl.out_f32, box_rows);
     if (rc) return rc;

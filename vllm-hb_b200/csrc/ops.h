@@ -9,14 +9,10 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag = nullptr, int window = 0, const float* rope_inv_freq = nullptr,
-                    int fresh_tokens = -1);
+                    hb_dtype dtype, int* err_flag = nullptr, int window = 0, int fresh_tokens = -1);
 // fresh_tokens >= 0: at most that many tokens at the end of every sequence were written by the
 // kernels launched right before this one; blocks of older tokens may be fetched before those
 // kernels have completed (programmatic launch).  -1: nothing is fetched early.
-// rope_inv_freq != null: q is the [q | k | v] projection row BEFORE RoPE; the kernel rotates q
-// on the fly and appends the rotated k and the v of the new token (position ctx-1) to the pool.
-// Only where paged_attention_mma_supported() holds.
 bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                    int nrep, int head_dim, int64_t num_blocks, int hkv, hb_dtype dtype);
 // Opts the tensor-core attention kernel in to its shared memory (once per device,

@@ -1,38 +1,96 @@
-// hb_fused_rowparallel: row-parallel projection + sum over ranks + residual + RMSNorm.
+// hb_fused_rowparallel: row-parallel projection + sum over ranks + residual + RMSNorm,
 //
-// Two implementations live behind the entry point:
-//   - the UNFUSED sequence  GEMM -> all-reduce -> add + RMSNorm  (three launches), which
-//     is what the reference runs (src/engine/arch/llama_tp.rs:327,533-552) and is kept
-//     as the measured baseline (algo = HB_ALGO_NCCL uses ncclAllReduce for the middle
-//     step, as src/parallel/comm.rs:83-166 does);
-//   - the fused kernel of rowpar_fused.cu (one launch per rank).
+//   resid_out  = resid_in + SUM_ranks( X_r . W_r^T )
+//   normed_out = rms_norm(resid_out; norm_w, eps)
+//
+// the steps o_proj/down_proj -> all_reduce -> residual -> next norm of the reference
+// (src/engine/arch/llama_tp.rs:327,533-552 and :339,563-571,517-522).  Four forms, picked
+// by world size, shape and `algo`, and reported by hb_fused_rowparallel_form():
+//   HB_ROWPAR_SINGLE   one rank: tcgen05 GEMM, then add + RMSNorm.
+//   HB_ROWPAR_PUSH     the GEMM epilogue pushes every 128-feature tile of its partial over
+//                      NVLink into the staging of the rank that reduces that column slice and
+//                      raises the tile's arrival flag (gemm_tc.cu, kEpiPush); one peer-memory
+//                      kernel then sums its slices, adds the residual, returns the reduced
+//                      slices to all ranks and normalises (ar_norm.cu).  Two launches; the
+//                      first hop of the all-reduce is inside the GEMM.
+//   HB_ROWPAR_EXCHANGE tcgen05 GEMM to a local partial, then the same peer-memory kernel
+//                      doing both hops (one-shot for small messages).
+//   HB_ROWPAR_NCCL     GEMM -> ncclAllReduce -> add + RMSNorm: the reference's sequence
+//                      (src/parallel/comm.rs:83-166), kept as the measured baseline.
+#include "rowpar.h"
+
+#include <algorithm>
+
 #include "comm.h"
 #include "common.h"
 #include "gemm.h"
-#include "rowpar.h"
 
 namespace hb {
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
-size_t rowpar_unfused_workspace_bytes(int64_t M, int64_t N, int64_t K_local) {
-  size_t ws = align256((size_t)M * N * 2);
+// Plans the GEMM with the push epilogue; false when the shape cannot take that form.
+static bool plan_push(TcGemmPlan* pl, const hb_world* w, const void* X, const void* W, int64_t M, int64_t N,
+                      int64_t K_local) {
+  if (!w || w->ws < 2 || !push_exchange_supported(w, M, N, HB_BF16)) return false;
+  if (!gemm_tc_supported(M, N, K_local, HB_BF16)) return false;
+  if (gemm_tc_plan(pl, X, W, M, N, K_local, kEpiPush, false, w->device) != HB_OK) return false;
+  return pl->cluster && pl->m_tiles == 1 &&
+         ((M + pl->m_pad / pl->splits - 1) / (pl->m_pad / pl->splits)) * (N / 128) <= kMaxPushFlags;
+}
+
+int rowpar_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_algo algo) {
+  if (M < 1 || N < 1 || K_local < 1) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: bad shape");
+  if (!w || w->ws == 1) return HB_ROWPAR_SINGLE;
+  if (algo == HB_ALGO_NCCL) return HB_ROWPAR_NCCL;
+  if (!w->attached) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: world not attached to its peers yet");
+  if (algo == HB_ALGO_AUTO || algo == HB_ALGO_TWO_SHOT) {
+    // two hops pay from 128 KiB (and three ranks) on; below that one hop of everything
+    const bool two_hop = algo == HB_ALGO_TWO_SHOT || (w->ws > 2 && (size_t)M * N * 2 > 128 * 1024);
+    alignas(16) static char dummy[16];
+    TcGemmPlan pl;
+    if (two_hop && plan_push(&pl, w, dummy, dummy, M, N, K_local)) return HB_ROWPAR_PUSH;
+  }
+  if (ar_add_norm_supported(w, M, N, HB_BF16)) return HB_ROWPAR_EXCHANGE;
+  return fail(HB_ERR_INVALID_ARG,
+              "fused row-parallel: %lld x %lld is outside the exchange kernel's range (rows <= 256, rows of at "
+              "most 32 KiB in multiples of 16 bytes); use HB_ALGO_NCCL", (long long)M, (long long)N);
+}
+
+size_t rowpar_workspace_bytes(int64_t M, int64_t N, int64_t K_local) {
+  size_t ws = align256((size_t)M * N * 2);  // the local partial of the forms that keep one
   ws += hb_gemm_workspace_bytes(M, N, K_local, HB_BF16);
   return ws + 256;
 }
 
-int rowpar_unfused(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* X,
-                   const void* W, const void* resid_in, const void* norm_w, int64_t M, int64_t N,
-                   int64_t K_local, float eps, hb_algo algo, void* workspace) {
+int rowpar_run(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* X, const void* W,
+               const void* resid_in, const void* norm_w, int64_t M, int64_t N, int64_t K_local, float eps,
+               hb_algo algo, void* workspace) {
+  const int form = rowpar_form(w, M, N, K_local, algo);
+  if (form < 0) return form;
+  if (w) HB_CUDA_CHECK(cudaSetDevice(w->device));
   uint8_t* base = (uint8_t*)workspace;
   void* partial = base;
   void* gemm_ws = base + align256((size_t)M * N * 2);
-  int rc = hb_gemm(st, partial, X, W, M, N, K_local, HB_BF16, gemm_ws);
-  if (rc) return rc;
-  if (w && w->ws > 1) {
-    rc = world_all_reduce(w, st, partial, (size_t)M * N, HB_BF16, algo);
-    if (rc) return rc;
+  int rc;
+  if (form == HB_ROWPAR_PUSH) {
+    TcGemmPlan pl;
+    if (!plan_push(&pl, w, X, W, M, N, K_local)) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: plan changed");
+    TcNormLink link;
+    link.push_peers = w->peer;
+    link.push_ranks = w->ws;
+    link.push_rank = w->rank;
+    link.push_spin = w->wait_limit;
+    if ((rc = gemm_tc_run(pl, st, nullptr, N, gemm_ws, nullptr, &link))) return rc;
+    PushGeometry geo{pl.m_pad / pl.splits, (int)(N / 128 / w->ws)};
+    return world_ar_add_norm(w, st, normed_out, resid_out, nullptr, resid_in, norm_w, M, N, eps, HB_BF16,
+                             HB_ALGO_TWO_SHOT, &geo);
   }
+  if ((rc = hb_gemm(st, partial, X, W, M, N, K_local, HB_BF16, gemm_ws))) return rc;
+  if (form == HB_ROWPAR_EXCHANGE)
+    return world_ar_add_norm(w, st, normed_out, resid_out, partial, resid_in, norm_w, M, N, eps, HB_BF16,
+                             algo == HB_ALGO_TWO_SHOT ? HB_ALGO_AUTO : algo);
+  if (form == HB_ROWPAR_NCCL && (rc = world_all_reduce(w, st, partial, (size_t)M * N, HB_BF16, HB_ALGO_NCCL))) return rc;
   return hb_add_rms_norm(st, normed_out, resid_out, partial, resid_in, norm_w, M, N, eps, HB_BF16);
 }
 
@@ -42,8 +100,11 @@ extern "C" {
 
 size_t hb_fused_rowparallel_workspace_bytes(int64_t M, int64_t N, int64_t K_local) {
   if (M <= 0 || N <= 0 || K_local <= 0) return 0;
-  return std::max(hb::rowpar_unfused_workspace_bytes(M, N, K_local),
-                  hb::rowpar_fused_workspace_bytes(M, N, K_local));
+  return hb::rowpar_workspace_bytes(M, N, K_local);
+}
+
+int hb_fused_rowparallel_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_algo algo) {
+  return hb::rowpar_form(w, M, N, K_local, algo);
 }
 
 int hb_fused_rowparallel(hb_world* w, void* stream, void* normed_out, void* resid_out,
@@ -53,12 +114,8 @@ int hb_fused_rowparallel(hb_world* w, void* stream, void* normed_out, void* resi
   HB_CHECK_ARG(resid_out && X && W && resid_in && workspace, "hb_fused_rowparallel: null pointer");
   HB_CHECK_ARG(!normed_out || norm_w, "hb_fused_rowparallel: normed_out needs a norm weight");
   HB_CHECK_ARG(M > 0 && N > 0 && K_local > 0, "hb_fused_rowparallel: bad shape");
-  auto st = (cudaStream_t)stream;
-  if (algo != HB_ALGO_NCCL && hb::rowpar_fused_supported(w, M, N, K_local))
-    return hb::rowpar_fused(w, st, normed_out, resid_out, X, W, resid_in, norm_w, M, N, K_local, eps,
-                            algo, workspace);
-  return hb::rowpar_unfused(w, st, normed_out, resid_out, X, W, resid_in, norm_w, M, N, K_local, eps,
-                            algo, workspace);
+  return hb::rowpar_run(w, (cudaStream_t)stream, normed_out, resid_out, X, W, resid_in, norm_w, M, N, K_local,
+                        eps, algo, workspace);
 }
 
 }  // extern "C"

@@ -16,6 +16,23 @@
 
 namespace hb {
 
+// A JSON number that is a non-negative integer small enough to be exact in a double.
+static bool as_index(const Json& j, uint64_t* out) {
+  if (j.kind != Json::Num) return false;
+  const double v = j.num;
+  if (!(v >= 0.0) || v > 9007199254740992.0 || v != (double)(uint64_t)v) return false;
+  *out = (uint64_t)v;
+  return true;
+}
+
+static size_t st_elem_size(const std::string& dt) {
+  if (dt == "F64" || dt == "I64" || dt == "U64") return 8;
+  if (dt == "F32" || dt == "I32" || dt == "U32") return 4;
+  if (dt == "F16" || dt == "BF16" || dt == "I16" || dt == "U16") return 2;
+  if (dt == "I8" || dt == "U8" || dt == "BOOL" || dt == "F8_E4M3" || dt == "F8_E5M2") return 1;
+  return 0;  // unknown: the size cannot be checked here
+}
+
 SafetensorsFile::~SafetensorsFile() {
   if (map_) munmap(map_, size_);
 }
@@ -53,14 +70,29 @@ int SafetensorsFile::open(const std::string& path) {
     const Json* dt = t.get("dtype");
     const Json* sh = t.get("shape");
     const Json* off = t.get("data_offsets");
-    if (!dt || !sh || !off || off->arr.size() != 2)
+    if (!dt || !sh || !off || dt->kind != Json::Str || sh->kind != Json::Arr || off->kind != Json::Arr ||
+        off->arr.size() != 2)
       return fail(HB_ERR_IO, "%s: tensor %s has a malformed entry", path.c_str(), kv.first.c_str());
     StTensor st_t;
     st_t.dtype = dt->str;
-    for (auto& d : sh->arr) st_t.shape.push_back((int64_t)d.num);
-    const size_t b = (size_t)off->arr[0].num, e = (size_t)off->arr[1].num;
+    uint64_t numel = 1;
+    for (auto& d : sh->arr) {
+      uint64_t v = 0;
+      if (!as_index(d, &v) || (v != 0 && numel > (1ull << 53) / v))
+        return fail(HB_ERR_IO, "%s: tensor %s has a bad shape entry", path.c_str(), kv.first.c_str());
+      numel *= v;
+      st_t.shape.push_back((int64_t)v);
+    }
+    uint64_t b = 0, e = 0;
+    if (!as_index(off->arr[0], &b) || !as_index(off->arr[1], &e))
+      return fail(HB_ERR_IO, "%s: tensor %s has bad data_offsets", path.c_str(), kv.first.c_str());
     if (e < b || e > data_len)
       return fail(HB_ERR_IO, "%s: tensor %s points outside the file", path.c_str(), kv.first.c_str());
+    const size_t es = st_elem_size(st_t.dtype);
+    if (es && (e - b) != numel * es)
+      return fail(HB_ERR_IO, "%s: tensor %s holds %llu bytes, its shape and dtype %s need %llu", path.c_str(),
+                  kv.first.c_str(), (unsigned long long)(e - b), st_t.dtype.c_str(),
+                  (unsigned long long)(numel * es));
     st_t.data = data0 + b;
     st_t.nbytes = e - b;
     tensors_[kv.first] = std::move(st_t);

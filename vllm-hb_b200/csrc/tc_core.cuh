@@ -55,6 +55,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// The same load with an L2 eviction policy (see l2_policy_*): weights are read once per step
+// and should leave L2 first, the batch operand is re-read by every CTA and should stay.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+// Asks the memory system to bring one box of the tensor map into L2; no shared memory, no
+// barrier, nothing to wait for.  Same 16-byte rule for x as the load.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tm, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tm), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 // Bulk tensor store shared -> global (box of the tensor map at element coordinates
 // x, y); rows and columns outside the tensor are clipped.  x * element size must be a
 // multiple of 16 bytes and the coordinates non-negative.
@@ -147,15 +173,6 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t caddr, float v) {
 }
 __device__ __forceinline__ void st_cluster_v4(uint32_t caddr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-// Bulk asynchronous copy from this CTA's shared memory into a cluster partner's; the bytes
-// are counted on the partner's mbarrier (both destination operands are shared::cluster
-// addresses from cluster_map()).  16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_copy_to_partner(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
-                                                     uint32_t bar_cluster) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster)
                : "memory");
 }
 // Every thread of every CTA of the cluster arrives; hardware barrier, always reached.
