@@ -445,6 +445,36 @@ int hb_forward(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t se
  * [B, vocab]) may be NULL.  Copies in and out happen inside the call. */
 int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,
                     uint32_t* next_tokens, float* logits_opt);
+/* ---- the step driven by a scheduler's block tables.  The reference's scheduler computes
+ * block tables, copy-on-write pairs and swap lists every step (SchedulerOutputs,
+ * src/scheduler/mod.rs:40-61,203-208; BlockManager::append_slot / swap_in / swap_out,
+ * src/scheduler/block_manager.rs:314-406) and its worker drops them
+ * (src/worker/mod.rs:250-305).  These entry points consume them: the caller (hb_bm_* or the
+ * Rust BlockManager itself) owns the block ids, the engine's KV pool is indexed by them.
+ * An engine is driven either through hb_seq handles or through tables, not both at once
+ * (the hb_seq allocator hands out ids of the same pool).
+ *
+ * hb_decode_batch_tables: row b feeds last_tokens[b] at absolute position positions[b]
+ * (= prompt_len + output_len - 1, src/worker/mod.rs:404-409) of the sequence whose table is
+ * block_tables[b * table_stride ...]; the table must cover that position
+ * (entries 0 .. positions[b]/16).  copy_pairs = blocks_to_copy as (src, dst) ids, applied
+ * to every layer's K and V before the step.  Outputs as hb_decode_batch.
+ * hb_forward_tables: n tokens of ONE sequence at positions seq_pos .. seq_pos+n-1; with
+ * seq_pos > 0 the positions below it must already hold this sequence's K/V in the
+ * table's blocks — a prefix-cache hit (hit_blocks * 16 tokens are skipped:
+ * src/scheduler/block_manager.rs:213-234), or a continued prefill.
+ * hb_kv_copy_blocks: dst := src for every pair (all layers, K and V).
+ * hb_kv_swap_blocks: swap_out (to_cpu != 0, pairs (gpu, cpu)) / swap_in (pairs (cpu, gpu))
+ * between the pool and a pinned host pool of hb_engine_reserve_cpu_blocks() blocks. */
+int hb_decode_batch_tables(hb_engine* e, size_t B, const uint32_t* last_tokens, const int64_t* positions,
+                           const int64_t* block_tables, size_t table_stride, const int64_t* copy_pairs,
+                           size_t n_copies, uint32_t* next_tokens, float* logits_opt);
+int hb_forward_tables(hb_engine* e, const uint32_t* ids, size_t n, size_t seq_pos, const int64_t* block_table,
+                      size_t table_len, float* logits_out);
+int hb_kv_copy_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs);
+int hb_engine_reserve_cpu_blocks(hb_engine* e, int64_t n_blocks);
+int hb_kv_swap_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs, int to_cpu);
+
 /* One decode step with CUDA events between its kernels — captured into a graph with an
  * event-record node after every kernel and replayed, so the kernels run back to back as in
  * a normal step (HB_PROFILE_EAGER=1 or HB_NO_GRAPH=1: issued kernel by kernel on the

@@ -162,12 +162,13 @@ class MixtralOracle:
         probs = K.rnd(K.softmax_last(logits.astype(np.float64)).astype(np.float32), dt)
         # The reference picks the top-k with an unstable sort (mixtral.rs:395-397): which expert
         # wins a tie, or a gap smaller than the arithmetic noise, is unspecified.  The smallest
-        # gap between the last chosen and the first rejected probability is recorded so that a
-        # parity test can tell a different-but-legal choice from an error.
+        # gap between the last chosen and the first rejected probability of the LAST token
+        # (the one whose logits are returned; earlier tokens reach it only through attention)
+        # is recorded so that a parity test can tell a different-but-legal choice from an error.
         k = self.cfg.num_experts_per_tok
         if probs.shape[1] > k:
-            srt = np.sort(probs, axis=1)[:, ::-1]
-            self.min_route_gap = min(self.min_route_gap, float(np.min(srt[:, k - 1] - srt[:, k])))
+            srt = np.sort(probs[-1])[::-1]
+            self.min_route_gap = min(self.min_route_gap, float(srt[k - 1] - srt[k]))
         return [route(probs[t], k) for t in range(x.shape[0])]
 
     def moe_partial(self, rank, x, layer, routes):

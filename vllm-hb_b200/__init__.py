@@ -166,6 +166,11 @@ _SIGS = {
     "hb_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "hb_decode_batch": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
     "hb_engine_profile_step": (_i, [_vp, _vp, _sz, _vp, _vp, _vp]),
+    "hb_decode_batch_tables": (_i, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp]),
+    "hb_forward_tables": (_i, [_vp, _vp, _sz, _sz, _vp, _sz, _vp]),
+    "hb_kv_copy_blocks": (_i, [_vp, _vp, _sz]),
+    "hb_engine_reserve_cpu_blocks": (_i, [_vp, _i64]),
+    "hb_kv_swap_blocks": (_i, [_vp, _vp, _sz, _i]),
     "hb_engine_gemm_bytes": (C.c_double, [_vp, _i64]),
     "hb_engine_last_step_ms": (_f, [_vp]),
     "hb_engine_last_step_launches": (_i64, [_vp]),
@@ -767,6 +772,44 @@ class Engine:
         check(lib.hb_decode_batch(self.handle, arr, B, last.ctypes.data, next_tokens.ctypes.data,
                                   logits.ctypes.data if logits is not None else None))
         return next_tokens
+
+    # --- the step driven by a scheduler's block tables
+    def decode_batch_tables(self, last_tokens, positions, block_tables, copy_pairs=(), logits=None) -> np.ndarray:
+        """One decode step for rows whose KV lives in the caller's block tables
+        (block_tables: int64 [B, stride], row b covers positions[b]); copy_pairs are the
+        scheduler's copy-on-write (src, dst) block pairs, applied first."""
+        last = np.ascontiguousarray(np.asarray(last_tokens, dtype=np.uint32))
+        pos = np.ascontiguousarray(np.asarray(positions, dtype=np.int64))
+        tab = np.ascontiguousarray(np.asarray(block_tables, dtype=np.int64))
+        B = len(last)
+        assert tab.ndim == 2 and tab.shape[0] == B and len(pos) == B
+        pairs = np.ascontiguousarray(np.asarray(list(copy_pairs), dtype=np.int64).reshape(-1, 2))
+        nxt = np.empty(B, dtype=np.uint32)
+        check(lib.hb_decode_batch_tables(self.handle, B, last.ctypes.data, pos.ctypes.data, tab.ctypes.data, tab.shape[1],
+                                         pairs.ctypes.data if len(pairs) else None, len(pairs), nxt.ctypes.data,
+                                         logits.ctypes.data if logits is not None else None))
+        return nxt
+
+    def forward_tables(self, token_ids, seq_pos: int, block_table) -> np.ndarray:
+        """Logits of the last of `token_ids` fed at positions seq_pos.. of the sequence that owns
+        `block_table`; positions below seq_pos must already be in the table's blocks."""
+        ids = np.ascontiguousarray(np.asarray(token_ids, dtype=np.uint32))
+        tab = np.ascontiguousarray(np.asarray(block_table, dtype=np.int64))
+        out = np.empty(self.vocab_size(), dtype=np.float32)
+        check(lib.hb_forward_tables(self.handle, ids.ctypes.data, len(ids), seq_pos, tab.ctypes.data, len(tab),
+                                    out.ctypes.data))
+        return out
+
+    def kv_copy_blocks(self, pairs) -> None:
+        p = np.ascontiguousarray(np.asarray(list(pairs), dtype=np.int64).reshape(-1, 2))
+        check(lib.hb_kv_copy_blocks(self.handle, p.ctypes.data if len(p) else None, len(p)))
+
+    def reserve_cpu_blocks(self, n: int) -> None:
+        check(lib.hb_engine_reserve_cpu_blocks(self.handle, n))
+
+    def kv_swap_blocks(self, pairs, to_cpu: bool) -> None:
+        p = np.ascontiguousarray(np.asarray(list(pairs), dtype=np.int64).reshape(-1, 2))
+        check(lib.hb_kv_swap_blocks(self.handle, p.ctypes.data if len(p) else None, len(p), 1 if to_cpu else 0))
 
     PROFILE_KINDS = ("gemm_qkv", "attention", "rope_kv", "norm", "other", "all_reduce",
                      "gemm_o_proj", "gemm_gate_up", "gemm_down", "gemm_lm_head")

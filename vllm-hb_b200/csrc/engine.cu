@@ -53,6 +53,7 @@ struct NamedTensor {
 };
 
 enum GemmKind { kQkv = 0, kO = 1, kGateUp = 2, kDown = 3, kLmHead = 4 };
+constexpr int kPairCap = 1024;  // block pairs per copy launch
 
 struct StepPlans {
   std::vector<TcGemmPlan> layer;  // [L * 4]
@@ -116,6 +117,9 @@ struct hb_engine {
   void* d_gemm_ws = nullptr;
   size_t gemm_ws_bytes = 0;
   int* d_err = nullptr;
+  int64_t* d_pairs = nullptr;   // (src, dst) block ids of a copy request, kPairCap pairs at a time
+  uint8_t* h_swap = nullptr;    // pinned CPU block pool [cpu_blocks][L][K|V][block bytes] (hb_engine_reserve_cpu_blocks)
+  int64_t cpu_blocks = 0;
   bool use_tc = false, use_graph = true, fused_swiglu = true;
   std::map<int, hb::StepPlans> plans;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -342,6 +346,7 @@ static int alloc_runtime(hb_engine* e, const hb_model_config* cfg) {
   if ((rc = dev_alloc(e, (void**)&e->d_next, (size_t)B * 4))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_err, 16))) return rc;
   HB_CUDA_CHECK(cudaMemset(e->d_err, 0, 16));
+  if ((rc = dev_alloc(e, (void**)&e->d_pairs, (size_t)kPairCap * 2 * sizeof(int64_t)))) return rc;
   std::vector<float> inv(e->hd / 2);
   if ((rc = hb_rope_inv_freq((float)e->theta, (int)e->hd, inv.data()))) return rc;
   if ((rc = dev_alloc(e, (void**)&e->d_inv_freq, inv.size() * 4))) return rc;
@@ -706,7 +711,8 @@ static int seq_ensure_block(hb_engine* e, hb_seq* s, int64_t pos) {
 // (row i then attends to the keys of rows 0..i, which the same step wrote before its
 // attention kernel runs: causal attention over the growing cache, llama_tp.rs:313-316).
 struct StepRow {
-  hb_seq* s;
+  const int64_t* blocks;  // the sequence's block table (ids into the KV pool), table[pos / 16]
+  size_t n_blocks;
   int64_t pos;
   uint32_t tok;
 };
@@ -724,9 +730,12 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
     if (!s) return fail(HB_ERR_INVALID_ARG, "null sequence at index %d", b);
     for (int j = 0; j < b; ++j)
       if (seqs[j] == s) return fail(HB_ERR_INVALID_ARG, "sequence repeated in one batch");
-    rows[b] = {s, s->len, tokens[b]};
   }
-  int rc = run_rows(e, rows.data(), B, next_tokens, logits_out, 0);
+  int rc;
+  for (int b = 0; b < B; ++b)
+    if ((rc = seq_ensure_block(e, seqs[b], seqs[b]->len))) return rc;
+  for (int b = 0; b < B; ++b) rows[b] = {seqs[b]->blocks.data(), seqs[b]->blocks.size(), seqs[b]->len, tokens[b]};
+  rc = run_rows(e, rows.data(), B, next_tokens, logits_out, 0);
   if (rc) return rc;
   for (int b = 0; b < B; ++b) seqs[b]->len += 1;
   return HB_OK;
@@ -740,9 +749,11 @@ static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float
   while (done < n) {
     const int c = (int)std::min<size_t>(n - done, (size_t)e->max_batch);
     rows.resize((size_t)c);
-    for (int i = 0; i < c; ++i) rows[i] = {s, s->len + i, ids[done + i]};
+    int rc;
+    if ((rc = seq_ensure_block(e, s, s->len + c - 1))) return rc;
+    for (int i = 0; i < c; ++i) rows[i] = {s->blocks.data(), s->blocks.size(), s->len + i, ids[done + i]};
     const bool last = done + (size_t)c == n;
-    int rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
     if (rc) return rc;
     s->len += c;
     done += (size_t)c;
@@ -759,17 +770,28 @@ static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tok
   int32_t* h_ctx = (int32_t*)(e->h_inputs + e->off_ctx);
   int64_t* h_slots = (int64_t*)(e->h_inputs + e->off_slots);
   int32_t* h_tables = (int32_t*)(e->h_inputs + e->off_tables);
-  for (int b = 0; b < B; ++b)
-    if ((rc = seq_ensure_block(e, rows[b].s, rows[b].pos))) return rc;
   for (int b = 0; b < B; ++b) {
-    hb_seq* s = rows[b].s;
-    const int64_t pos = rows[b].pos;
-    h_ids[b] = rows[b].tok;
+    const StepRow& r = rows[b];
+    const int64_t pos = r.pos;
+    // the reference's embedding lookup fails on an id outside the vocabulary
+    // (index_select, llama_tp.rs:213-216); so does this
+    if ((int64_t)r.tok >= e->V)
+      return fail(HB_ERR_INVALID_ARG, "token id %u at row %d is outside the vocabulary of %lld", r.tok, b,
+                  (long long)e->V);
+    const int64_t need = pos / HB_BLOCK_SIZE + 1;
+    if (pos < 0 || (int64_t)r.n_blocks < need || need > e->max_blocks_per_seq)
+      return fail(HB_ERR_INVALID_ARG, "row %d: a block table of %zu block(s) does not cover position %lld", b,
+                  r.n_blocks, (long long)pos);
+    for (int64_t i = 0; i < need; ++i)
+      if (r.blocks[i] < 0 || r.blocks[i] >= e->num_blocks)
+        return fail(HB_ERR_INVALID_ARG, "row %d: block id %lld outside the pool of %lld", b, (long long)r.blocks[i],
+                    (long long)e->num_blocks);
+    h_ids[b] = r.tok;
     h_pos[b] = (int32_t)pos;
     h_ctx[b] = (int32_t)(pos + 1);
-    h_slots[b] = s->blocks[pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + pos % HB_BLOCK_SIZE;
+    h_slots[b] = r.blocks[pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + pos % HB_BLOCK_SIZE;
     int32_t* row = h_tables + (size_t)b * e->max_blocks_per_seq;
-    for (size_t i = 0; i < s->blocks.size(); ++i) row[i] = (int32_t)s->blocks[i];
+    for (int64_t i = 0; i < need; ++i) row[i] = (int32_t)r.blocks[i];
   }
   StepPlans* sp = nullptr;
   if ((rc = ensure_plans(e, B, &sp))) return rc;
@@ -869,6 +891,7 @@ int hb_engine_free(hb_engine* e) {
   for (auto& kv : e->plans)
     if (kv.second.graph) cudaGraphExecDestroy(kv.second.graph);
   for (void* p : e->allocations) cudaFree(p);
+  if (e->h_swap) cudaFreeHost(e->h_swap);
   if (e->h_inputs) cudaFreeHost(e->h_inputs);
   if (e->h_next) cudaFreeHost(e->h_next);
   if (e->ev0) cudaEventDestroy(e->ev0);
@@ -1135,6 +1158,113 @@ int hb_decode_batch(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t*
                     uint32_t* next_tokens, float* logits_opt) {
   HB_CHECK_ARG(e && seqs && last_tokens, "hb_decode_batch: null argument");
   return hb::decode_step(e, seqs, (int)B, last_tokens, next_tokens, logits_opt);
+}
+
+// ---- the same step driven by a scheduler's own block tables (src/scheduler/mod.rs:40-61,
+// 203-208 emits them, with copy-on-write pairs and swap lists; src/worker/mod.rs:250-305
+// never consumes them)
+int hb_kv_copy_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs) {
+  HB_CHECK_ARG(e && (pairs || n_pairs == 0), "hb_kv_copy_blocks: null argument");
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
+  const int64_t block_bytes = e->hkv_l * HB_BLOCK_SIZE * e->hd * (int64_t)e->es;
+  for (size_t i = 0; i < 2 * n_pairs; ++i)
+    if (pairs[i] < 0 || pairs[i] >= e->num_blocks)
+      return hb::fail(HB_ERR_INVALID_ARG, "hb_kv_copy_blocks: block id %lld outside the pool of %lld",
+                      (long long)pairs[i], (long long)e->num_blocks);
+  for (size_t done = 0; done < n_pairs; done += hb::kPairCap) {
+    const size_t n = std::min<size_t>(hb::kPairCap, n_pairs - done);
+    HB_CUDA_CHECK(cudaMemcpyAsync(e->d_pairs, pairs + 2 * done, n * 2 * sizeof(int64_t), cudaMemcpyHostToDevice, e->stream));
+    for (int64_t l = 0; l < e->L; ++l) {
+      int rc = hb::kv_copy_blocks(e->stream, e->kc[l], e->vc[l], e->d_pairs, (int64_t)n, block_bytes, e->num_blocks);
+      if (rc) return rc;
+    }
+    HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));  // `pairs` and d_pairs may be reused
+  }
+  return HB_OK;
+}
+
+int hb_engine_reserve_cpu_blocks(hb_engine* e, int64_t n_blocks) {
+  HB_CHECK_ARG(e && n_blocks >= 0, "hb_engine_reserve_cpu_blocks: bad argument");
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
+  if (e->h_swap) { cudaFreeHost(e->h_swap); e->h_swap = nullptr; e->cpu_blocks = 0; }
+  if (n_blocks == 0) return HB_OK;
+  const size_t block_bytes = (size_t)e->hkv_l * HB_BLOCK_SIZE * e->hd * e->es;
+  HB_CUDA_CHECK(cudaMallocHost((void**)&e->h_swap, (size_t)n_blocks * e->L * 2 * block_bytes));
+  e->cpu_blocks = n_blocks;
+  return HB_OK;
+}
+
+int hb_kv_swap_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs, int to_cpu) {
+  HB_CHECK_ARG(e && (pairs || n_pairs == 0), "hb_kv_swap_blocks: null argument");
+  HB_CUDA_CHECK(cudaSetDevice(e->device));
+  const size_t block_bytes = (size_t)e->hkv_l * HB_BLOCK_SIZE * e->hd * e->es;
+  for (size_t i = 0; i < n_pairs; ++i) {
+    // swap_out pairs are (gpu, cpu), swap_in pairs (cpu, gpu): block_manager.rs:359-406
+    const int64_t g = to_cpu ? pairs[2 * i] : pairs[2 * i + 1], c = to_cpu ? pairs[2 * i + 1] : pairs[2 * i];
+    if (g < 0 || g >= e->num_blocks || c < 0 || c >= e->cpu_blocks)
+      return hb::fail(HB_ERR_INVALID_ARG, "hb_kv_swap_blocks: pair %zu (gpu %lld, cpu %lld) outside the pools (%lld, %lld)",
+                      i, (long long)g, (long long)c, (long long)e->num_blocks, (long long)e->cpu_blocks);
+  }
+  for (size_t i = 0; i < n_pairs; ++i) {
+    const int64_t g = to_cpu ? pairs[2 * i] : pairs[2 * i + 1], c = to_cpu ? pairs[2 * i + 1] : pairs[2 * i];
+    for (int64_t l = 0; l < e->L; ++l)
+      for (int kv = 0; kv < 2; ++kv) {
+        uint8_t* dev = (uint8_t*)(kv ? e->vc[l] : e->kc[l]) + (size_t)g * block_bytes;
+        uint8_t* host = e->h_swap + (((size_t)c * e->L + l) * 2 + kv) * block_bytes;
+        if (to_cpu) HB_CUDA_CHECK(cudaMemcpyAsync(host, dev, block_bytes, cudaMemcpyDeviceToHost, e->stream));
+        else HB_CUDA_CHECK(cudaMemcpyAsync(dev, host, block_bytes, cudaMemcpyHostToDevice, e->stream));
+      }
+  }
+  HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
+  return HB_OK;
+}
+
+int hb_decode_batch_tables(hb_engine* e, size_t B, const uint32_t* last_tokens, const int64_t* positions,
+                           const int64_t* block_tables, size_t table_stride, const int64_t* copy_pairs,
+                           size_t n_copies, uint32_t* next_tokens, float* logits_opt) {
+  HB_CHECK_ARG(e && last_tokens && positions && block_tables, "hb_decode_batch_tables: null argument");
+  if (B == 0 || (int)B > e->max_batch)
+    return hb::fail(HB_ERR_INVALID_ARG, "batch %zu outside [1, %d]", B, e->max_batch);
+  int rc;
+  // blocks_to_copy first: a sequence that shared its last block writes into its own copy
+  if (n_copies && (rc = hb_kv_copy_blocks(e, copy_pairs, n_copies))) return rc;
+  std::vector<hb::StepRow> rows(B);
+  for (size_t b = 0; b < B; ++b) {
+    if (positions[b] < 0) return hb::fail(HB_ERR_INVALID_ARG, "row %zu: negative position", b);
+    const size_t covered = std::min<size_t>(table_stride, (size_t)(positions[b] / HB_BLOCK_SIZE + 1));
+    rows[b] = {block_tables + b * table_stride, covered, positions[b], last_tokens[b]};
+  }
+  // two rows of one decode step are two sequences: they never write the same KV slot
+  for (size_t b = 0; b < B; ++b) {
+    if (rows[b].n_blocks * HB_BLOCK_SIZE <= (size_t)rows[b].pos) continue;  // reported by run_rows
+    const int64_t slot = rows[b].blocks[rows[b].pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + rows[b].pos % HB_BLOCK_SIZE;
+    for (size_t j = 0; j < b; ++j) {
+      if (rows[j].n_blocks * HB_BLOCK_SIZE <= (size_t)rows[j].pos) continue;
+      if (rows[j].blocks[rows[j].pos / HB_BLOCK_SIZE] * HB_BLOCK_SIZE + rows[j].pos % HB_BLOCK_SIZE == slot)
+        return hb::fail(HB_ERR_INVALID_ARG, "rows %zu and %zu write the same KV slot %lld", j, b, (long long)slot);
+    }
+  }
+  return hb::run_rows(e, rows.data(), (int)B, next_tokens, logits_opt, 0);
+}
+
+int hb_forward_tables(hb_engine* e, const uint32_t* ids, size_t n, size_t seq_pos, const int64_t* block_table,
+                      size_t table_len, float* logits_out) {
+  if (n == 0) return hb::fail(HB_ERR_EMPTY, "hb_forward_tables: token list is empty");
+  HB_CHECK_ARG(e && ids && block_table && logits_out, "hb_forward_tables: null argument");
+  // chunks of consecutive positions, as hb_forward; positions below seq_pos must already hold
+  // this sequence's K/V in the table's blocks (a prefix-cache hit: block_manager.rs:213-234)
+  std::vector<hb::StepRow> rows;
+  size_t done = 0;
+  while (done < n) {
+    const int c = (int)std::min<size_t>(n - done, (size_t)e->max_batch);
+    rows.resize((size_t)c);
+    for (int i = 0; i < c; ++i) rows[i] = {block_table, table_len, (int64_t)(seq_pos + done) + i, ids[done + i]};
+    const bool last = done + (size_t)c == n;
+    int rc = hb::run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    if (rc) return rc;
+    done += (size_t)c;
+  }
+  return HB_OK;
 }
 
 int hb_engine_profile_step(hb_engine* e, hb_seq* const* seqs, size_t B, const uint32_t* last_tokens,

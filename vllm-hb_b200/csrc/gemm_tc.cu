@@ -802,8 +802,14 @@ static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
   return s;
 }
 
+// Tuning hook (not part of the public interface): overrides the split factor, the pipeline
+// budget (1 = 200 KB / one CTA per SM, 2 = 110 KB) and the batch rows per tile of every
+// plan made afterwards; all zero restores the planner's own choice.
+static int g_plan_override[3] = {0, 0, 0};
+
 int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
                  int epilogue, bool out_f32, int device, int force_splits) {
+  if (g_plan_override[0] > 0) force_splits = g_plan_override[0];
   if (!gemm_tc_supported(M, N, K, HB_BF16))
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: unsupported shape M=%lld N=%lld K=%lld", (long long)M,
                 (long long)N, (long long)K);
@@ -826,6 +832,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const int m_cap = n_acc == 2 ? 128 : 256;
   const int64_t m_eff = std::min<int64_t>(M, m_cap);
   pl.m_pad = (int)std::max<int64_t>(16, (m_eff + 15) / 16 * 16);
+  if (g_plan_override[2] > 0) pl.m_pad = std::min(pl.m_pad, std::max(16, g_plan_override[2] / 16 * 16));
   pl.m_tiles = (int)((M + pl.m_pad - 1) / pl.m_pad);
   pl.n_tiles = (int)((n_rows + kTileN - 1) / kTileN);
   const int acc_cols = pl.m_pad * n_acc;
@@ -833,7 +840,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const size_t stage = (size_t)kTileN * kTileK * 2 * n_acc + (size_t)pl.m_pad * kTileK * 2;
   // two CTAs per SM when the stages allow it, so one CTA's epilogue hides under the
   // other's loads
-  const size_t budget = 110 * 1024;
+  const size_t budget = g_plan_override[1] == 1 ? 200 * 1024 : 110 * 1024;
   pl.stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, budget / stage));
   pl.smem_bytes = pl.stages * stage + 1024;
   if (pl.smem_bytes > di.smem_optin)
@@ -1043,6 +1050,12 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
 }
 
 }  // namespace hb
+
+extern "C" void hb_debug_gemm_override(int splits, int big, int m_pad) {
+  hb::g_plan_override[0] = splits;
+  hb::g_plan_override[1] = big;
+  hb::g_plan_override[2] = m_pad;
+}
 
 #ifdef HB_TC_TRACE
 extern "C" int hb_debug_tc_launches(unsigned long long* host_out, int n) {

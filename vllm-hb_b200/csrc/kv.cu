@@ -40,6 +40,34 @@ __global__ void kv_paged_kernel(V* __restrict__ kc, V* __restrict__ vc, const V*
 
 }  // namespace hb
 
+// One CTA per (pair, K or V): the whole block [nkv, 16, head_dim] of `src` is copied to
+// `dst` inside the same pool with 16-byte loads and stores.  Pairs with an id outside the
+// pool are skipped.
+__global__ void kv_copy_blocks_kernel(uint4* __restrict__ kc, uint4* __restrict__ vc,
+                                      const int64_t* __restrict__ pairs, int64_t block_vecs,
+                                      int64_t num_blocks) {
+  const int64_t src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+  if (src < 0 || dst < 0 || src >= num_blocks || dst >= num_blocks || src == dst) return;
+  uint4* pool = blockIdx.y == 0 ? kc : vc;
+  const uint4* s = pool + src * block_vecs;
+  uint4* d = pool + dst * block_vecs;
+  for (int64_t i = threadIdx.x; i < block_vecs; i += blockDim.x) d[i] = s[i];
+}
+
+namespace hb {
+
+int kv_copy_blocks(cudaStream_t st, void* k_cache, void* v_cache, const int64_t* d_pairs, int64_t n_pairs,
+                   int64_t block_bytes, int64_t num_blocks) {
+  if (n_pairs <= 0) return HB_OK;
+  if (block_bytes % 16) return fail(HB_ERR_INVALID_ARG, "kv_copy_blocks: block size must be a multiple of 16 bytes");
+  kv_copy_blocks_kernel<<<dim3((unsigned)n_pairs, 2), 256, 0, st>>>((uint4*)k_cache, (uint4*)v_cache, d_pairs,
+                                                                   block_bytes / 16, num_blocks);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+}  // namespace hb
+
 extern "C" {
 
 int hb_kv_assign_contig(void* stream, void* buf, const void* src, int nkv, int64_t max_seq,

@@ -19,6 +19,11 @@ bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* 
 // outside any stream capture).
 int paged_attention_mma_prepare();
 
+// dst block := src block for every (src, dst) pair (device array of 2 * n_pairs ids), in the K
+// and the V pool of one layer; a block is block_bytes long (kv.cu).
+int kv_copy_blocks(cudaStream_t st, void* k_cache, void* v_cache, const int64_t* d_pairs, int64_t n_pairs,
+                   int64_t block_bytes, int64_t num_blocks);
+
 // Mixture-of-experts routing (moe.cu): scale[m, e] = renormalised top-k softmax weight of
 // expert e for token m, 0 for the others; moe_scale_act multiplies act[m, e*inter + i] by it.
 int moe_route(cudaStream_t st, float* scale, const void* x, const void* w_gate, int64_t n_tokens,
