@@ -403,10 +403,10 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
         auto& w0 = e->layers[0];
         if ((rc = gemm_tc_plan(&probe_o, e->d_attn, w0.wo, B, e->H, e->hq_l * e->hd, kEpiPush, false, e->device))) return rc;
         if ((rc = gemm_tc_plan(&probe_d, e->d_act, w0.wdown, B, e->H, e->I_e, kEpiPush, false, e->device))) return rc;
-        sp.push = probe_o.cluster && probe_d.cluster && probe_o.m_tiles == 1 && probe_d.m_tiles == 1;
         const int tiles = (int)(e->H / 128 / e->ws);
-        sp.geo_o = {probe_o.m_pad / probe_o.splits, tiles};
-        sp.geo_down = {probe_d.m_pad / probe_d.splits, tiles};
+        sp.geo_o = {gemm_tc_push_row_block(probe_o), tiles};
+        sp.geo_down = {gemm_tc_push_row_block(probe_d), tiles};
+        sp.push = sp.geo_o.row_block > 0 && sp.geo_down.row_block > 0;
       }
     }
     const int row_epi = sp.defer_norm ? kEpiResidual : (sp.push ? kEpiPush : kEpiStore);

@@ -103,6 +103,10 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
 // err_flag (device int, may be null) is set non-zero when a bounded wait ran out.
 // True when `plan` can carry the RoPE + KV-write epilogue of TcNormLink.
 bool gemm_tc_rope_epilogue_ok(const TcGemmPlan& plan);
+// Batch rows per arrival flag of a kEpiPush plan (the PushGeometry::row_block its consumer
+// needs): the rows a cluster partner owns, or the whole batch tile of an unsplit plan; 0 when
+// the plan cannot push.
+int gemm_tc_push_row_block(const TcGemmPlan& plan);
 int gemm_tc_run(const TcGemmPlan& plan, cudaStream_t st, void* Y, int64_t ldy, void* workspace,
                 int* err_flag, const TcNormLink* link = nullptr);
 

@@ -130,6 +130,27 @@ __device__ __forceinline__ void tc_launch_trace(int id, int what, int n, int k) 
 #define TC_LAUNCH_TRACE(what) do { } while (0)
 #endif
 
+// kEpiPush: the first hop of the all-reduce.  The CTA's staged bf16 tile [n_rows][128] (batch
+// rows row0.. of output tile `tile`) goes with 16-byte stores into the staging of the rank
+// that reduces this tile's column slice (peer memory over NVLink, or this rank's own), then
+// the arrival flag of (row block, this rank, tile of the slice) is raised there with a
+// system-scope release.  Every thread of the CTA calls it.
+__device__ __forceinline__ void push_tile(const TcParams& p, const uint8_t* staged, int row0, int n_rows, int tile,
+                                          int row_block, uint32_t seq, int tid) {
+  const int R = p.push_R, me = p.push_me, T = p.push_T;
+  const int q = tile / T, ti = tile % T;
+  uint4* dst = reinterpret_cast<uint4*>((uint8_t*)p.push_peer[q] + kFlagBytes) +
+               ((int64_t)me * p.M + row0) * p.push_sv + ti * 16;
+  const uint4* src = reinterpret_cast<const uint4*>(staged);
+  for (int idx = tid; idx < n_rows * 16; idx += kTcThreads) {
+    const int rr = idx >> 4, vv = idx & 15;
+    if (row0 + rr < p.M) dst[(int64_t)rr * p.push_sv + vv] = src[idx];
+  }
+  __syncthreads();  // orders every thread's stores before the release below
+  if (tid == 0)
+    peer_st_release(&reinterpret_cast<CommFlags*>(p.push_peer[q])->tflag[(row_block * R + me) * T + ti], seq + 1);
+}
+
 // ----------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -549,27 +570,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // this tile's column slice (16-byte stores into its staging over NVLink, or into this
       // rank's own), then the tile's arrival flag is raised there
       store_y = false;
-      const int R = p.push_R, me = p.push_me, T = p.push_T;
-      const int q = tile / T, ti = tile % T;
-      CommFlags* fl = reinterpret_cast<CommFlags*>(p.push_peer[me]);
       // s_seq / s_push_ok were written by warp 3 before the epilogue's first CTA barrier
-      const uint32_t seq = s_seq;
-      const bool go = tail_ok && s_push_ok != 0;
-      if (go) {
+      if (tail_ok && s_push_ok != 0) {
         const int row0 = m_base + split * CW;
-        uint4* dst = reinterpret_cast<uint4*>((uint8_t*)p.push_peer[q] + kFlagBytes) +
-                     ((int64_t)me * p.M + row0) * p.push_sv + ti * 16;
-        const uint4* src = reinterpret_cast<const uint4*>(smem_gen + out_off);
-        for (int idx = tid; idx < CW * 16; idx += kTcThreads) {
-          const int rr = idx >> 4, vv = idx & 15;
-          if (row0 + rr < p.M) dst[(int64_t)rr * p.push_sv + vv] = src[idx];
-        }
-        __syncthreads();  // orders every thread's stores before the release below
-        if (tid == 0)
-          peer_st_release(&reinterpret_cast<CommFlags*>(p.push_peer[q])->tflag[((row0 / CW) * R + me) * T + ti],
-                          seq + 1);
+        push_tile(p, smem_gen + out_off, row0, CW, tile, row0 / CW, s_seq, tid);
       } else if (tid == 0 && tail_ok) {
-        atomicExch(&fl->status, HB_ERR_TIMEOUT);
+        atomicExch(&reinterpret_cast<CommFlags*>(p.push_peer[p.push_me])->status, HB_ERR_TIMEOUT);
         if (p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
       }
     }
@@ -625,7 +631,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       }
       fence_async_smem();
       __syncthreads();
-      if (tid == 0) {
+      if (p.epilogue == kEpiPush) {
+        // the whole [m_pad][128] tile is staged at once (the host checks that it fits): push it
+        if (s_push_ok != 0) {
+          push_tile(p, smem_gen, m_base, p.m_pad, tile, m_tile, s_seq, tid);
+        } else if (tid == 0) {
+          atomicExch(&reinterpret_cast<CommFlags*>(p.push_peer[p.push_me])->status, HB_ERR_TIMEOUT);
+          if (p.err_flag) atomicExch(p.err_flag, HB_ERR_TIMEOUT);
+        }
+      } else if (tid == 0) {
         for (int g = g0; g < g1; ++g)
           if (m_base + g * 16 < p.M)
             tma_store_2d(&tm_y, smem_base + (uint32_t)(g - g0) * grp_bytes, tile * kTileN, m_base + g * 16);
@@ -832,27 +846,64 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   const int m_cap = n_acc == 2 ? 128 : 256;
   const int64_t m_eff = std::min<int64_t>(M, m_cap);
   pl.m_pad = (int)std::max<int64_t>(16, (m_eff + 15) / 16 * 16);
+  pl.n_tiles = (int)((n_rows + kTileN - 1) / kTileN);
+  const int k_chunks = (int)(K / kTileK);
+  const char* cl_env = getenv("HB_TC_CLUSTER");
+  const bool want_cluster = !(cl_env && cl_env[0] == '0');
+  const bool tuned = want_cluster && force_splits <= 0 && g_plan_override[1] == 0 && g_plan_override[2] == 0;
+  // Few weights under a wide batch (o_proj and q|k|v at high tensor-parallel degrees): the
+  // split-K exchange moves 128 x m_pad fp32 per CTA through the SM-to-SM network, which at
+  // m_pad = 128 costs more than the matrix takes to stream.  Two batch tiles of 64 rows read
+  // the weight tile twice (the second time from L2) and need no, or a smaller, exchange
+  // (measured: 8192 x 1024 at M = 128 15.4 -> 11.1 us, 1280 x 8192 19.0 -> 16.4 us).
+  bool m_split = false;
+  if (tuned && n_acc == 1 && pl.m_pad >= 128 && (int64_t)pl.n_tiles * k_chunks <= 2048 &&
+      (epilogue == kEpiStore || epilogue == kEpiPush)) {
+    pl.m_pad = 64;
+    m_split = true;
+  }
   if (g_plan_override[2] > 0) pl.m_pad = std::min(pl.m_pad, std::max(16, g_plan_override[2] / 16 * 16));
   pl.m_tiles = (int)((M + pl.m_pad - 1) / pl.m_pad);
-  pl.n_tiles = (int)((n_rows + kTileN - 1) / kTileN);
+  const int units = pl.n_tiles * pl.m_tiles;
   const int acc_cols = pl.m_pad * n_acc;
   pl.tmem_cols = acc_cols <= 32 ? 32 : acc_cols <= 64 ? 64 : acc_cols <= 128 ? 128 : acc_cols <= 256 ? 256 : 512;
   const size_t stage = (size_t)kTileN * kTileK * 2 * n_acc + (size_t)pl.m_pad * kTileK * 2;
-  // two CTAs per SM when the stages allow it, so one CTA's epilogue hides under the
-  // other's loads
-  const size_t budget = g_plan_override[1] == 1 ? 200 * 1024 : 110 * 1024;
-  pl.stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, budget / stage));
-  pl.smem_bytes = pl.stages * stage + 1024;
-  if (pl.smem_bytes > di.smem_optin)
-    return fail(HB_ERR_INVALID_ARG, "gemm_tc: needs %zu bytes of shared memory", pl.smem_bytes);
-  const int ctas_per_sm = std::max(1, std::min<int>((int)(di.smem_optin / pl.smem_bytes), 512 / pl.tmem_cols));
-  const int k_chunks = (int)(K / kTileK);
-  const int slots = di.sm_count * std::min(ctas_per_sm, 2);
-  const char* cl_env = getenv("HB_TC_CLUSTER");
-  const bool want_cluster = !(cl_env && cl_env[0] == '0');
-  if (force_splits > 0) pl.splits = std::min(force_splits, k_chunks);
-  else if (want_cluster) pl.splits = pick_cluster_splits(pl.n_tiles * pl.m_tiles, k_chunks, di.sm_count);
-  else pl.splits = pick_splits(pl.n_tiles * pl.m_tiles, k_chunks, slots);
+  // Two pipeline depths: ~110 KB, so that two CTAs share an SM and one's epilogue hides under
+  // the other's loads, or ~200 KB with the SM to itself.
+  const size_t small_budget = 110 * 1024, big_budget = 200 * 1024;
+  auto stages_for = [&](size_t budget) { return (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, budget / stage)); };
+  const int small_stages = stages_for(small_budget);
+  const int big_stages = (size_t)stages_for(big_budget) * stage + 1024 <= di.smem_optin ? stages_for(big_budget) : small_stages;
+  if ((size_t)small_stages * stage + 1024 > di.smem_optin)
+    return fail(HB_ERR_INVALID_ARG, "gemm_tc: needs %zu bytes of shared memory", (size_t)small_stages * stage + 1024);
+  const int slots = di.sm_count * 2;
+  bool big = g_plan_override[1] == 1;
+  if (force_splits > 0) {
+    pl.splits = std::min(force_splits, k_chunks);
+  } else if (!want_cluster) {
+    pl.splits = pick_splits(units, k_chunks, slots);
+  } else if (tuned && n_acc == 2 && units <= di.sm_count) {
+    // SwiGLU tiles carry two weight slabs per stage: the 110 KB budget holds two stages, too
+    // shallow to keep HBM busy.  One CTA per SM with the deep pipeline, and the largest split
+    // that still fits one wave (measured: 14336 x 8192 at M = 128 68.6 -> 51.0 us)
+    int sp = 1;
+    while (sp * 2 <= 8 && units * sp * 2 <= di.sm_count && k_chunks / (sp * 4) >= 4) sp *= 2;
+    pl.splits = sp;
+    big = true;
+  } else if (m_split) {
+    // split K only while a CTA would stream more than 512 KB or the SMs are not covered
+    int sp = 1;
+    auto cta_bytes = [&](int s_) { return (size_t)(kTileN + pl.m_pad) * (size_t)(k_chunks / s_) * kTileK * 2; };
+    while (sp < 8 && k_chunks / (sp * 2) >= 4 &&
+           (units * sp * 5 < di.sm_count * 4 || (cta_bytes(sp) > 512 * 1024 && units * sp < 2 * di.sm_count)))
+      sp *= 2;
+    pl.splits = sp;
+  } else {
+    pl.splits = pick_cluster_splits(units, k_chunks, di.sm_count);
+  }
+  // a grid of at most one CTA per SM gains nothing from leaving room for a second one
+  if (tuned && units * pl.splits <= di.sm_count) big = true;
+  pl.stages = big ? big_stages : small_stages;
   // cluster form: power-of-two size <= 8 whose receive buffers fit the pipeline's
   // shared memory; anything else reduces through global scratch
   pl.cluster = false;
@@ -869,39 +920,33 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   if (want_cluster && pl.splits > 1 && pl.tma_store) {
     // The exchange buffers of a wide batch (or of the two SwiGLU accumulators) may not
     // fit the two-CTAs-per-SM budget.  When a split factor yields at most one CTA per SM
-    // anyway, it may take a deeper pipeline (one CTA per SM) instead of being halved: a
-    // matrix with few row slabs needs the splits to reach the SMs.
+    // anyway, it may take the deep pipeline instead of being halved: a matrix with few row
+    // slabs needs the splits to reach the SMs.
     if (force_splits <= 0) {
-      const int small_stages = pl.stages;
-      const size_t big = 200 * 1024;
-      const int big_stages = (int)std::max<size_t>(2, std::min<size_t>(kMaxStages, big / stage));
-      const bool big_ok = big_stages > small_stages &&
-                          (size_t)big_stages * stage + 1024 <= di.smem_optin;
       while (pl.splits > 1) {
         if (pl.m_pad / pl.splits >= 4 && pl.m_pad % (4 * pl.splits) == 0) {
-          pl.stages = small_stages;
+          pl.stages = big ? big_stages : small_stages;
           if (recv_fits(pl.splits)) break;
-          if (big_ok && (int64_t)pl.n_tiles * pl.m_tiles * pl.splits <= di.sm_count) {
+          if (big_stages > small_stages && (int64_t)units * pl.splits <= di.sm_count) {
             pl.stages = big_stages;
             if (recv_fits(pl.splits)) break;
           }
         }
-        pl.stages = small_stages;
         pl.splits /= 2;
       }
-      pl.smem_bytes = pl.stages * stage + 1024;
+      if (pl.splits == 1) pl.stages = (tuned && units <= di.sm_count) ? big_stages : small_stages;
     }
     // every partner owns m_pad / splits batch rows, exchanged four at a time
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
                  pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
+  pl.smem_bytes = pl.stages * stage + 1024;
   pl.l2_burst = 0;
-  const size_t units = (size_t)pl.m_tiles * pl.n_tiles;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
   // partials where they expect zeroed counters.
-  if (!pl.cluster && units * sizeof(int) > kCounterBlockBytes) pl.splits = 1;
-  pl.ws_partials_bytes = (pl.splits > 1 && !pl.cluster) ? units * pl.splits * n_acc * pl.m_pad * kTileN * sizeof(float) : 0;
+  if (!pl.cluster && (size_t)units * sizeof(int) > kCounterBlockBytes) pl.splits = 1;
+  pl.ws_partials_bytes = (pl.splits > 1 && !pl.cluster) ? (size_t)units * pl.splits * n_acc * pl.m_pad * kTileN * sizeof(float) : 0;
   pl.ws_counters_bytes = (pl.splits > 1 && !pl.cluster) ? kCounterBlockBytes : 0;
   // opt in to the large dynamic shared memory window once per device (here, not at
   // launch, so that launches stay legal inside a stream capture)
@@ -922,6 +967,15 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   if (rc) return rc;
   rc = encode_map(&pl.tm_x, X, M, K, pl.m_pad);
   return rc;
+}
+
+int gemm_tc_push_row_block(const TcGemmPlan& pl) {
+  if (pl.epilogue != kEpiPush || pl.out_f32 || !pl.tma_store) return 0;
+  if (pl.cluster && pl.splits > 1) return pl.m_pad / pl.splits;
+  // one CTA per tile: the whole [m_pad][128] bf16 tile must fit the pipeline buffers
+  const size_t stage = (size_t)kTileN * kTileK * 2 + (size_t)pl.m_pad * kTileK * 2;
+  if (pl.splits == 1 && (size_t)pl.m_pad * kTileN * 2 <= (size_t)pl.stages * stage) return pl.m_pad;
+  return 0;
 }
 
 bool gemm_tc_rope_epilogue_ok(const TcGemmPlan& pl) {
@@ -964,11 +1018,11 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.tma_store = (pl.tma_store && y_ok && (pl.cluster || pl.splits == 1)) ? 1 : 0;
   if (push) {
     const int R = link ? link->push_ranks : 0;
-    if (!pl.cluster || pl.m_tiles != 1 || pl.out_f32 || !link || !link->push_peers || R < 2 || R > HB_MAX_RANKS ||
+    const int rb = gemm_tc_push_row_block(pl);
+    if (rb < 1 || pl.out_f32 || !link || !link->push_peers || R < 2 || R > HB_MAX_RANKS ||
         link->push_rank < 0 || link->push_rank >= R || pl.N % ((int64_t)R * kTileN) ||
-        pl.m_pad / pl.splits < 1 ||
-        (int64_t)((pl.M + pl.m_pad / pl.splits - 1) / (pl.m_pad / pl.splits)) * (pl.N / kTileN) > kMaxPushFlags)
-      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the push epilogue needs a cluster plan, bf16 output and rank slices of whole tiles");
+        (int64_t)((pl.M + rb - 1) / rb) * (pl.N / kTileN) > kMaxPushFlags)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the push epilogue needs bf16 output staged as whole tiles and rank slices of whole tiles");
     for (int q = 0; q < R; ++q) p.push_peer[q] = link->push_peers[q];
     p.push_R = R;
     p.push_me = link->push_rank;

@@ -35,8 +35,8 @@ static bool plan_push(TcGemmPlan* pl, const hb_world* w, const void* X, const vo
   if (!w || w->ws < 2 || !push_exchange_supported(w, M, N, HB_BF16)) return false;
   if (!gemm_tc_supported(M, N, K_local, HB_BF16)) return false;
   if (gemm_tc_plan(pl, X, W, M, N, K_local, kEpiPush, false, w->device) != HB_OK) return false;
-  return pl->cluster && pl->m_tiles == 1 &&
-         ((M + pl->m_pad / pl->splits - 1) / (pl->m_pad / pl->splits)) * (N / 128) <= kMaxPushFlags;
+  const int rb = gemm_tc_push_row_block(*pl);
+  return rb > 0 && ((M + rb - 1) / rb) * (N / 128) <= kMaxPushFlags;
 }
 
 int rowpar_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_algo algo) {
@@ -82,7 +82,7 @@ int rowpar_run(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, 
     link.push_rank = w->rank;
     link.push_spin = w->wait_limit;
     if ((rc = gemm_tc_run(pl, st, nullptr, N, gemm_ws, nullptr, &link))) return rc;
-    PushGeometry geo{pl.m_pad / pl.splits, (int)(N / 128 / w->ws)};
+    PushGeometry geo{gemm_tc_push_row_block(pl), (int)(N / 128 / w->ws)};
     return world_ar_add_norm(w, st, normed_out, resid_out, nullptr, resid_in, norm_w, M, N, eps, HB_BF16,
                              HB_ALGO_TWO_SHOT, &geo);
   }
