@@ -203,6 +203,26 @@ int hb_embed(void* stream, void* out, const void* table, const uint32_t* ids, in
 int hb_argmax(void* stream, uint32_t* out, const void* logits, int64_t n, int64_t vocab,
               hb_dtype dtype);
 
+/* Sampling on the device (src/sampling/mod.rs:30-113): per row of logits [n, vocab] (fp32,
+ * device) the reference's pipeline — presence/frequency penalties from token_counts
+ * (uint32 [n, vocab] device, may be NULL: src/sampling/penalty.rs:28-52), division by the
+ * temperature, softmax, top-p nucleus filter, renormalisation (src/sampling/nucleus.rs:7-62)
+ * — without copying a row to the host.  temperature < 1e-6 is greedy: the delta distribution
+ * on the first maximum (mod.rs:79-88).  The nucleus is every token whose probability is at
+ * least that of the token at which the descending cumulative mass reaches top_p (tokens tied
+ * with it are all kept; the reference's unstable sort keeps an unspecified subset of them).
+ * hb_logits_to_probs writes the distribution (what the speculative decoder's acceptance
+ * test reads, src/speculative.rs:189-196); hb_sample also draws tokens[i] from row i: the
+ * first index whose cumulative probability exceeds u_i, u_i = the top 24 bits of
+ * splitmix64(seeds[i]) / 2^24 (the reference draws with rand's SmallRng + WeightedIndex; that
+ * stream is not reproduced, only its distribution).  probs_workspace: n * vocab floats. */
+int hb_logits_to_probs(void* stream, float* probs, const float* logits, const uint32_t* token_counts, int64_t n,
+                       int64_t vocab, float temperature, float top_p, float presence_penalty,
+                       float frequency_penalty);
+int hb_sample(void* stream, uint32_t* tokens, float* probs_workspace, const float* logits,
+              const uint32_t* token_counts, const uint64_t* seeds, int64_t n, int64_t vocab, float temperature,
+              float top_p, float presence_penalty, float frequency_penalty);
+
 /* --------------------------------------------------------------- comm surface */
 
 /* One rank's membership of a tensor-parallel group: the replacement of TpWorld
@@ -258,10 +278,7 @@ int hb_world_status(hb_world* w);
  * afterwards; a step already captured in a CUDA graph keeps the limit it was captured
  * with.  (No counterpart in the reference: NCCL's own watchdog plays this part there.) */
 int hb_world_set_wait_limit(hb_world* w, uint32_t polls);
-/* on != 0: the exchange kernels signal early that the next kernel of the stream may become
- * resident (programmatic dependent launch), so that a GEMM launched after them requests
- * its weights while the exchange waits for its peers.  Off by default. */
-int hb_world_set_early_trigger(hb_world* w, int on);
+
 
 /* In-place SUM all-reduce of `count` elements at `buf` on this rank; every rank calls
  * it with the same count/dtype.  The result is valid on every rank (a superset of the
@@ -472,6 +489,15 @@ int hb_decode_batch_tables(hb_engine* e, size_t B, const uint32_t* last_tokens, 
 int hb_forward_tables(hb_engine* e, const uint32_t* ids, size_t n, size_t seq_pos, const int64_t* block_table,
                       size_t table_len, float* logits_out);
 int hb_kv_copy_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs);
+/* Speculative verification as ONE forward: the n tokens [last, draft_0 .. draft_{n-2}] are fed
+ * at positions seq_pos .. and the logits of EVERY position come back (host f32 [n, vocab]),
+ * where the reference runs up to K+1 single-token target forwards (src/speculative.rs:174-212).
+ * The caller applies the acceptance rule and then drops the rejected tokens' K/V with
+ * hb_seq_truncate(seq, seq_pos + accepted) (the reference stops feeding at the first
+ * rejection instead). */
+int hb_forward_all_positions(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t seq_pos,
+                             float* logits_out);
+int hb_seq_truncate(hb_engine* e, hb_seq* s, int64_t new_len);
 int hb_engine_reserve_cpu_blocks(hb_engine* e, int64_t n_blocks);
 int hb_kv_swap_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs, int to_cpu);
 

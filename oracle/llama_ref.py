@@ -245,9 +245,9 @@ def random_weights(cfg: LlamaTpConfig, seed: int = 1, std: float = 0.02, norm_on
     return out
 
 
-def write_model(path: str, cfg: LlamaTpConfig, weights: dict, model_type: str = "llama") -> None:
-    """config.json + model.safetensors (F32) as Engine::load reads them
-    (src/engine/loader.rs:105-126)."""
+def write_model(path: str, cfg: LlamaTpConfig, weights: dict, model_type: str = "llama", dtype: str = "F32") -> None:
+    """config.json + model.safetensors (F32, or BF16 / F16 as checkpoints ship) as Engine::load
+    reads them (src/engine/loader.rs:105-126)."""
     os.makedirs(path, exist_ok=True)
     conf = dict(model_type=model_type, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
                 num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
@@ -255,17 +255,23 @@ def write_model(path: str, cfg: LlamaTpConfig, weights: dict, model_type: str = 
                 rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta)
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(conf, f)
-    write_safetensors(os.path.join(path, "model.safetensors"), weights)
+    write_safetensors(os.path.join(path, "model.safetensors"), weights, dtype)
 
 
-def write_safetensors(file_path: str, weights: dict) -> None:
-    """One F32 safetensors file: u64 header length, JSON header, raw little-endian data."""
+def write_safetensors(file_path: str, weights: dict, dtype: str = "F32") -> None:
+    """One safetensors file: u64 header length, JSON header, raw little-endian data."""
     header, blobs, off = {}, [], 0
     for name in sorted(weights):
         a = np.ascontiguousarray(weights[name], dtype=np.float32)
-        header[name] = {"dtype": "F32", "shape": list(a.shape), "data_offsets": [off, off + a.nbytes]}
-        blobs.append(a.tobytes())
-        off += a.nbytes
+        if dtype == "BF16":
+            raw = K.to_bf16_bits(a).tobytes()
+        elif dtype == "F16":
+            raw = a.astype(np.float16).tobytes()
+        else:
+            raw = a.tobytes()
+        header[name] = {"dtype": dtype, "shape": list(a.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
     hjson = json.dumps(header, separators=(",", ":")).encode()
     hjson += b" " * ((8 - len(hjson) % 8) % 8)
     with open(file_path, "wb") as f:

@@ -118,6 +118,24 @@ def test_tiny_bf16_logits(hb, cuda, tiny):
     eng.close()
 
 
+@pytest.mark.parametrize("file_dtype,engine", [("BF16", "bf16"), ("F16", "bf16"), ("F32", "bf16"), ("BF16", "f32")])
+def test_checkpoint_dtypes(hb, cuda, tiny, tmp_path, file_dtype, engine):
+    """Checkpoints in bf16 (native: the slices go from the mapped file to the device as they
+    are) and in other dtypes (converted on the device): the tensors on the device equal the
+    file's values rounded to the engine dtype, bit for bit."""
+    from oracle import kernels_ref as K
+
+    cfg, weights, _ = tiny
+    R.write_model(str(tmp_path), cfg, weights, dtype=file_dtype)
+    eng = hb.Engine.load(str(tmp_path), max_seq_len=32, bf16=engine == "bf16", force_f32=engine == "f32", max_batch=2)
+    for name in ("model.layers.1.mlp.down_proj.weight", "model.layers.0.self_attn.k_proj.weight", "model.norm.weight",
+                 "lm_head.weight"):
+        in_file = K.rnd(weights[name], {"BF16": "bf16", "F16": "f16", "F32": "f32"}[file_dtype])
+        want = K.rnd(in_file, engine)
+        assert np.array_equal(eng.get_tensor(name).reshape(want.shape), want), name
+    eng.close()
+
+
 def test_engine_errors(hb, cuda, tiny, tmp_path):
     cfg, weights, path = tiny
     with pytest.raises(hb.HbError) as ei:
@@ -134,6 +152,60 @@ def test_engine_errors(hb, cuda, tiny, tmp_path):
         eng.forward_with_cache(list(range(40)), 0, seq)  # needs 3 blocks, pool has 2
     assert ei.value.code == hb.ERR_OOM_BLOCKS
     eng.close()
+
+
+def rewrite_header(src_dir, dst_dir, edit):
+    """Copy a model directory, passing the safetensors JSON header through `edit`."""
+    import json
+    import os
+    import shutil
+
+    os.makedirs(dst_dir, exist_ok=True)
+    shutil.copy(os.path.join(src_dir, "config.json"), dst_dir)
+    raw = open(os.path.join(src_dir, "model.safetensors"), "rb").read()
+    hlen = int.from_bytes(raw[:8], "little")
+    header = json.loads(raw[8:8 + hlen])
+    edit(header)
+    h = json.dumps(header, separators=(",", ":")).encode()
+    h += b" " * ((8 - len(h) % 8) % 8)
+    with open(os.path.join(dst_dir, "model.safetensors"), "wb") as f:
+        f.write(len(h).to_bytes(8, "little") + h + raw[8 + hlen:])
+    return str(dst_dir)
+
+
+def test_malformed_checkpoints_are_refused(hb, cuda, tiny, tmp_path):
+    """A header whose offsets, shapes or sizes do not add up ends in HB_ERR_IO, never in a read
+    past the mapping or a silently mis-sharded tensor."""
+    cfg, weights, path = tiny
+    name = "model.layers.0.self_attn.q_proj.weight"
+
+    def truncated(h):        # fewer bytes than shape x dtype
+        b, e = h[name]["data_offsets"]
+        h[name]["data_offsets"] = [b, e - 64]
+
+    def transposed(h):       # right element count, wrong shape: must not be sharded as if it were right
+        name2 = "model.layers.0.mlp.down_proj.weight"
+        h[name2]["shape"] = h[name2]["shape"][::-1]
+
+    def negative(h):
+        h[name]["shape"] = [-256, -256]
+
+    def fractional(h):
+        b, e = h[name]["data_offsets"]
+        h[name]["data_offsets"] = [b + 0.5, e]
+
+    def past_the_end(h):
+        b, e = h[name]["data_offsets"]
+        h[name]["data_offsets"] = [b + 10 ** 12, e + 10 ** 12]
+
+    def mislabelled(h):      # same bytes declared as a 2-byte type
+        h[name]["dtype"] = "BF16"
+
+    for i, edit in enumerate((truncated, transposed, negative, fractional, past_the_end, mislabelled)):
+        bad = rewrite_header(path, tmp_path / f"bad{i}", edit)
+        with pytest.raises(hb.HbError) as ei:
+            hb.Engine.load(bad, max_seq_len=32, bf16=False, force_f32=True, max_batch=2)
+        assert ei.value.code == hb.ERR_IO, (edit.__name__, ei.value.msg)
 
 
 SHAPE_TC = dict(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,

@@ -205,6 +205,28 @@ def test_paged_attention_ignores_garbage_past_context(hb, cuda):
     assert np.array_equal(got, ref) and np.all(np.isfinite(got))
 
 
+@pytest.mark.parametrize("dtype,hq,hkv,hd", [("bf16", 8, 2, 128), ("f32", 4, 2, 64)])
+def test_paged_attention_context_at_table_capacity(hb, cuda, dtype, hq, hkv, hd):
+    """A context that fills its table row to the last slot (ctx == max_blocks * 16) is read in
+    full; a context CLAIMED longer than the row can describe is cut to the row, so that the
+    next sequence's table entries are never taken for this sequence's blocks."""
+    rng = np.random.default_rng(3)
+    n_seqs, num_blocks, max_blocks = 3, 40, 4
+    q = K.rnd(rng.standard_normal((n_seqs, hq, hd)).astype(np.float32), dtype)
+    kc = K.rnd(rng.standard_normal((num_blocks, hkv, 16, hd)).astype(np.float32), dtype)
+    vc = K.rnd(rng.standard_normal((num_blocks, hkv, 16, hd)).astype(np.float32), dtype)
+    tables = np.stack([rng.permutation(num_blocks)[:max_blocks] for _ in range(n_seqs)]).astype(np.int32)
+    full = np.array([max_blocks * 16, 5, max_blocks * 16], dtype=np.int32)
+    args = (dev(q, dtype, cuda), dev(kc, dtype, cuda), dev(vc, dtype, cuda), torch.from_numpy(tables).to(cuda))
+    for n_splits in (1, 2):
+        got = host(hb.paged_decode_attention(*args, torch.from_numpy(full).to(cuda), n_splits))
+        want = oracle_attention(q, kc, vc, tables, full, hkv)
+        assert rel_err(got, want.astype(np.float32)) <= TOL[dtype]
+        claimed = np.array([max_blocks * 16 + 40, 5, 10 ** 6], dtype=np.int32)   # host-validated: cut, not followed
+        cut = host(hb.paged_decode_attention(*args, torch.from_numpy(claimed).to(cuda), n_splits))
+        assert np.array_equal(cut, got)
+
+
 # -------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("M,N,K_", [(1, 256, 256), (8, 1024, 512), (64, 4096, 4096), (64, 6144, 4096), (33, 1000, 320),
                                     (128, 8192, 1024), (256, 512, 3584), (1, 128, 64), (17, 8, 64), (300, 256, 128),

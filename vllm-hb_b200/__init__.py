@@ -124,7 +124,6 @@ _SIGS = {
     "hb_world_stream": (_vp, [_vp]),
     "hb_world_status": (_i, [_vp]),
     "hb_world_set_wait_limit": (_i, [_vp, C.c_uint32]),
-    "hb_world_set_early_trigger": (_i, [_vp, _i]),
     "hb_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i]),
     "hb_all_reduce_add_rms_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i]),
     "hb_fused_rowparallel_workspace_bytes": (_sz, [_i64, _i64, _i64]),
@@ -169,6 +168,10 @@ _SIGS = {
     "hb_decode_batch_tables": (_i, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp]),
     "hb_forward_tables": (_i, [_vp, _vp, _sz, _sz, _vp, _sz, _vp]),
     "hb_kv_copy_blocks": (_i, [_vp, _vp, _sz]),
+    "hb_forward_all_positions": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
+    "hb_seq_truncate": (_i, [_vp, _vp, _i64]),
+    "hb_logits_to_probs": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _f, _f, _f, _f]),
+    "hb_sample": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _f, _f, _f]),
     "hb_engine_reserve_cpu_blocks": (_i, [_vp, _i64]),
     "hb_kv_swap_blocks": (_i, [_vp, _vp, _sz, _i]),
     "hb_engine_gemm_bytes": (C.c_double, [_vp, _i64]),
@@ -393,6 +396,31 @@ def gemm_ex(x, w, epilogue: int = 0, out_f32: bool = False, force_splits: int = 
     return y
 
 
+def logits_to_probs(logits, temperature: float, top_p: float = 1.0, token_counts=None, presence: float = 0.0,
+                    frequency: float = 0.0, stream=None):
+    """Sampling distribution of every row of `logits` (torch CUDA float32 [n, vocab])."""
+    import torch
+
+    n, vocab = logits.shape
+    probs = torch.empty_like(logits)
+    check(lib.hb_logits_to_probs(_stream(stream), _ptr(probs), _ptr(logits), _ptr(token_counts), n, vocab,
+                                 float(temperature), float(top_p), float(presence), float(frequency)))
+    return probs
+
+
+def sample(logits, seeds, temperature: float, top_p: float = 1.0, token_counts=None, presence: float = 0.0,
+           frequency: float = 0.0, stream=None):
+    """One token per row of `logits`, drawn on the device; seeds: torch CUDA uint64/int64 [n]."""
+    import torch
+
+    n, vocab = logits.shape
+    probs = torch.empty_like(logits)
+    out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    check(lib.hb_sample(_stream(stream), _ptr(out), _ptr(probs), _ptr(logits), _ptr(token_counts), _ptr(seeds), n,
+                        vocab, float(temperature), float(top_p), float(presence), float(frequency)))
+    return out, probs
+
+
 def silu_mul(gate_up, stream=None):
     import torch
 
@@ -517,9 +545,6 @@ class TpWorld:
     def set_wait_limit(self, polls: int) -> None:
         """Polls after which a device-side wait on a peer flag gives up (0 = default)."""
         check(lib.hb_world_set_wait_limit(self.handle, polls))
-
-    def set_early_trigger(self, on: bool) -> None:
-        check(lib.hb_world_set_early_trigger(self.handle, 1 if on else 0))
 
     def all_reduce(self, buf, algo: int = ALGO_AUTO, stream=None):
         """In-place SUM over ranks of a torch CUDA tensor (TpWorld::all_reduce)."""
@@ -799,6 +824,16 @@ class Engine:
         check(lib.hb_forward_tables(self.handle, ids.ctypes.data, len(ids), seq_pos, tab.ctypes.data, len(tab),
                                     out.ctypes.data))
         return out
+
+    def forward_all_positions(self, token_ids, seq_pos: int, cache: "Sequence_") -> np.ndarray:
+        """Logits [n, vocab] of every fed position in one forward (speculative verification)."""
+        ids = np.ascontiguousarray(np.asarray(token_ids, dtype=np.uint32))
+        out = np.empty((len(ids), self.vocab_size()), dtype=np.float32)
+        check(lib.hb_forward_all_positions(self.handle, cache.handle, ids.ctypes.data, len(ids), seq_pos, out.ctypes.data))
+        return out
+
+    def truncate(self, cache: "Sequence_", new_len: int) -> None:
+        check(lib.hb_seq_truncate(self.handle, cache.handle, new_len))
 
     def kv_copy_blocks(self, pairs) -> None:
         p = np.ascontiguousarray(np.asarray(list(pairs), dtype=np.int64).reshape(-1, 2))

@@ -458,11 +458,6 @@ int hb_world_set_wait_limit(hb_world* w, uint32_t polls) {
   return HB_OK;
 }
 
-int hb_world_set_early_trigger(hb_world* w, int on) {
-  HB_CHECK_ARG(w, "hb_world_set_early_trigger: null world");
-  w->trigger_early = on != 0;
-  return HB_OK;
-}
 
 int hb_all_reduce(hb_world* w, void* stream, void* buf, size_t count, hb_dtype dtype,
                   hb_algo algo) {

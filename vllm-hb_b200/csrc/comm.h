@@ -44,7 +44,6 @@ struct hb_world {
   bool attached = false;
   void* nccl = nullptr;               // ncclComm_t when hb_world_init_nccl ran
   uint32_t wait_limit = 1u << 22;     // polls before a device-side wait on a peer flag gives up
-  bool trigger_early = false;         // exchange kernels let their successor become resident while they wait
   int32_t* host_status = nullptr;     // pinned mirror for hb_world_status
 };
 

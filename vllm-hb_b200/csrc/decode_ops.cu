@@ -156,6 +156,32 @@ __global__ void to_f32_kernel(float* __restrict__ dst, const T* __restrict__ src
   if (idx < n) dst[idx] = to_f32<T>(src[(idx / cols) * src_ld + idx % cols]);
 }
 
+// dst[r * dst_ld + c] = convert(src[r * cols + c]) for a dense [rows, cols] source
+template <typename TD, typename TS>
+__global__ void convert_2d_kernel(TD* __restrict__ dst, const TS* __restrict__ src, int64_t n, int64_t cols,
+                                  int64_t dst_ld) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) dst[(idx / cols) * dst_ld + idx % cols] = from_f32<TD>(to_f32<TS>(src[idx]));
+}
+
+int convert_2d(cudaStream_t st, void* dst, hb_dtype dst_dtype, int64_t dst_ld, const void* src, hb_dtype src_dtype,
+               int64_t rows, int64_t cols) {
+  const int64_t n = rows * cols;
+  if (n == 0) return HB_OK;
+  if (dst_ld <= 0) dst_ld = cols;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  HB_DISPATCH_DTYPE(dst_dtype, TD, {
+    switch (src_dtype) {
+      case HB_F32: convert_2d_kernel<TD, float><<<grid, 256, 0, st>>>((TD*)dst, (const float*)src, n, cols, dst_ld); break;
+      case HB_F16: convert_2d_kernel<TD, __half><<<grid, 256, 0, st>>>((TD*)dst, (const __half*)src, n, cols, dst_ld); break;
+      case HB_BF16: convert_2d_kernel<TD, __nv_bfloat16><<<grid, 256, 0, st>>>((TD*)dst, (const __nv_bfloat16*)src, n, cols, dst_ld); break;
+      default: return fail(HB_ERR_UNSUPPORTED_DTYPE, "unsupported source dtype %d", (int)src_dtype);
+    }
+  });
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
 int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_t cols,
                 int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
                 float std, int64_t dst_ld) {

@@ -143,45 +143,48 @@ static int dev_alloc(hb_engine* e, void** p, size_t bytes) {
   return HB_OK;
 }
 
-static float src_to_f32(const uint8_t* p, const std::string& dt, int64_t i) {
-  if (dt == "F32") { float v; memcpy(&v, p + 4 * i, 4); return v; }
-  if (dt == "F16") { __half v; memcpy(&v, p + 2 * i, 2); return __half2float(v); }
-  uint16_t b; memcpy(&b, p + 2 * i, 2);  // BF16
-  uint32_t u = (uint32_t)b << 16; float v; memcpy(&v, &u, 4); return v;
-}
-
-static void f32_to_dst(uint8_t* d, hb_dtype dt, int64_t i, float v) {
-  if (dt == HB_F32) memcpy(d + 4 * i, &v, 4);
-  else if (dt == HB_F16) { __half h = __float2half_rn(v); memcpy(d + 2 * i, &h, 2); }
-  else { __nv_bfloat16 h = __float2bfloat16_rn(v); memcpy(d + 2 * i, &h, 2); }
-}
-
 static bool same_dtype(const std::string& s, hb_dtype d) {
   return (s == "F32" && d == HB_F32) || (s == "F16" && d == HB_F16) || (s == "BF16" && d == HB_BF16);
 }
 
-// Copy rows [r0, r0+nr) x cols [c0, c0+nc) of a host [rows, cols] tensor to device
-// memory at dst (row-major [nr, nc]) converting to the engine dtype — the narrow() of
-// column_shard / row_shard (src/parallel/shard.rs:46-74) followed by to_device.
-// dst_ld: row stride of the destination in elements (0 = nc, contiguous)
+static hb_dtype st_dtype(const std::string& s) { return s == "F32" ? HB_F32 : s == "F16" ? HB_F16 : HB_BF16; }
+
+// Rows [r0, r0+nr) x cols [c0, c0+nc) of a [rows, cols] tensor of the memory-mapped
+// checkpoint go to device memory at dst (row-major [nr, nc], row stride dst_ld elements) in
+// the engine dtype — the narrow() of column_shard / row_shard (src/parallel/shard.rs:46-74)
+// followed by to_device, without the reference's full CPU copy in the target dtype
+// (llama_tp.rs:367-377): only this rank's slice leaves the page cache, as one strided copy
+// straight from the mapping, and a checkpoint in another dtype is converted on the device.
+// `stage` is a device buffer that grows to the largest slice that needs converting.
+struct UploadStage {
+  void* buf = nullptr;
+  size_t bytes = 0;
+  ~UploadStage() { if (buf) cudaFree(buf); }
+};
+
 static int upload_slice(hb_engine* e, void* dst, const StTensor& t, int64_t cols, int64_t r0,
-                        int64_t nr, int64_t c0, int64_t nc, std::vector<uint8_t>* scratch, int64_t dst_ld = 0) {
-  scratch->resize((size_t)nr * nc * e->es);
-  uint8_t* s = scratch->data();
+                        int64_t nr, int64_t c0, int64_t nc, UploadStage* stage, int64_t dst_ld = 0) {
+  const size_t src_es = t.dtype == "F32" ? 4 : 2;
+  const uint8_t* src = t.data + ((size_t)r0 * cols + c0) * src_es;
+  if (dst_ld <= 0) dst_ld = nc;
   if (same_dtype(t.dtype, e->dtype)) {
-    for (int64_t r = 0; r < nr; ++r)
-      memcpy(s + (size_t)r * nc * e->es, t.data + ((size_t)(r0 + r) * cols + c0) * e->es, (size_t)nc * e->es);
-  } else {
-    for (int64_t r = 0; r < nr; ++r)
-      for (int64_t c = 0; c < nc; ++c)
-        f32_to_dst(s, e->dtype, r * nc + c, src_to_f32(t.data, t.dtype, (r0 + r) * cols + c0 + c));
-  }
-  if (dst_ld > 0 && dst_ld != nc) {
-    HB_CUDA_CHECK(cudaMemcpy2D(dst, (size_t)dst_ld * e->es, s, (size_t)nc * e->es, (size_t)nc * e->es, (size_t)nr,
+    HB_CUDA_CHECK(cudaMemcpy2D(dst, (size_t)dst_ld * e->es, src, (size_t)cols * src_es, (size_t)nc * src_es, (size_t)nr,
                                cudaMemcpyHostToDevice));
     return HB_OK;
   }
-  HB_CUDA_CHECK(cudaMemcpy(dst, s, scratch->size(), cudaMemcpyHostToDevice));
+  const size_t need = (size_t)nr * nc * src_es;
+  if (need > stage->bytes) {
+    if (stage->buf) cudaFree(stage->buf);
+    stage->buf = nullptr;
+    stage->bytes = 0;
+    HB_CUDA_CHECK(cudaMalloc(&stage->buf, need));
+    stage->bytes = need;
+  }
+  HB_CUDA_CHECK(cudaMemcpy2D(stage->buf, (size_t)nc * src_es, src, (size_t)cols * src_es, (size_t)nc * src_es, (size_t)nr,
+                             cudaMemcpyHostToDevice));
+  int rc = convert_2d(e->stream, dst, e->dtype, dst_ld, stage->buf, st_dtype(t.dtype), nr, nc);
+  if (rc) return rc;
+  HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));  // the stage is reused by the next slice
   return HB_OK;
 }
 
@@ -423,22 +426,6 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
       for (int k = 0; k < 4; ++k) ws = std::max(ws, sp.layer[l * 4 + k].workspace_bytes());
     }
     if ((rc = gemm_tc_plan(&sp.lm_head, e->d_x, e->lm_head, B, e->V, e->H, kEpiStore, true, e->device))) return rc;
-    if (e->ws > 1) {
-      // The GEMMs that follow an exchange (q|k|v after down_proj's, gate|up after o_proj's) may
-      // become resident while the exchange waits for its peers and HBM is idle: they then
-      // request this many MB of their weights into L2 ahead of their dependency wait.
-      static const int mb = [] { const char* v = getenv("HB_XCHG_PREFETCH_MB"); return v ? atoi(v) : 0; }();
-      if (mb > 0) {
-        hb_world_set_early_trigger(e->world, 1);
-        for (int64_t l = 0; l < e->L; ++l)
-          for (int kind : {(int)kQkv, (int)kGateUp}) {
-            TcGemmPlan& pl = sp.layer[l * 4 + kind];
-            const size_t ctas = (size_t)pl.n_tiles * pl.m_tiles * pl.splits;
-            const size_t chunk = (size_t)128 * 64 * 2 * (pl.epilogue == kEpiSwiGLU ? 2 : 1);
-            pl.l2_burst = (int)(((size_t)mb << 20) / (ctas * chunk));
-          }
-      }
-    }
     ws = std::max(ws, sp.lm_head.workspace_bytes());
     // RoPE and the KV write ride in the q|k|v GEMM epilogue when its output tile is one head
     // (HB_ROPE_EPI=0: the separate kernel)
@@ -743,7 +730,8 @@ static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t*
 
 // Prefill of `n` prompt tokens of one sequence in chunks of up to max_batch rows; the
 // logits of the last token go to logits_out (host [V]) when it is not null.
-static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float* logits_out) {
+static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float* logits_out,
+                   bool all_positions = false) {
   std::vector<StepRow> rows;
   size_t done = 0;
   while (done < n) {
@@ -753,7 +741,8 @@ static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float
     if ((rc = seq_ensure_block(e, s, s->len + c - 1))) return rc;
     for (int i = 0; i < c; ++i) rows[i] = {s->blocks.data(), s->blocks.size(), s->len + i, ids[done + i]};
     const bool last = done + (size_t)c == n;
-    rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    if (all_positions) rc = run_rows(e, rows.data(), c, nullptr, logits_out + done * (size_t)e->V, 0);
+    else rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
     if (rc) return rc;
     s->len += c;
     done += (size_t)c;
@@ -1006,7 +995,7 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
     for (auto& kv : shards.back()->tensors()) all[kv.first] = &kv.second;
   }
   hb_engine* g = e.get();
-  std::vector<uint8_t> scratch;
+  hb::UploadStage scratch;
   auto get = [&](const std::string& name, int64_t rows, int64_t cols, const hb::StTensor** t) -> int {
     auto it = all.find(name);
     if (it == all.end()) return hb::fail(HB_ERR_IO, "Weight not found: %s", name.c_str());  // llama_tp.rs:380-385
@@ -1147,6 +1136,30 @@ int hb_seq_free(hb_engine* e, hb_seq* s) {
 }
 
 int64_t hb_seq_len(const hb_seq* s) { return s ? s->len : -1; }
+
+int hb_seq_truncate(hb_engine* e, hb_seq* s, int64_t new_len) {
+  HB_CHECK_ARG(e && s, "hb_seq_truncate: null argument");
+  HB_CHECK_ARG(new_len >= 0 && new_len <= s->len, "hb_seq_truncate: length %lld outside [0, %lld]", (long long)new_len,
+               (long long)s->len);
+  s->len = new_len;
+  // blocks that hold no token any more go back to the free list (FIFO, as freed blocks do)
+  const size_t keep = (size_t)((new_len + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE);
+  while (s->blocks.size() > keep) {
+    e->free_blocks.push_back(s->blocks.back());
+    s->blocks.pop_back();
+  }
+  return HB_OK;
+}
+
+int hb_forward_all_positions(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, size_t seq_pos,
+                             float* logits_out) {
+  if (n == 0) return hb::fail(HB_ERR_EMPTY, "hb_forward_all_positions: token list is empty");
+  HB_CHECK_ARG(e && s && ids && logits_out, "hb_forward_all_positions: null argument");
+  if ((int64_t)seq_pos != s->len)
+    return hb::fail(HB_ERR_INVALID_ARG, "hb_forward_all_positions: seq_pos %zu but the sequence holds %lld tokens",
+                    seq_pos, (long long)s->len);
+  return hb::prefill(e, s, ids, n, logits_out, true);
+}
 
 int64_t hb_seq_block_table(const hb_seq* s, int64_t* out, int64_t cap) {
   if (!s) return HB_ERR_INVALID_ARG;

@@ -81,10 +81,6 @@ struct TcGemmPlan {
   bool cluster = false;  // the splits of a tile form a thread-block cluster (on-chip reduction)
   int stages = 0;
   int tmem_cols = 0;
-  // k-chunks per CTA requested into L2 before the dependency wait, after the ones that fill
-  // the shared-memory pipeline.  Set by the caller for a GEMM that follows a kernel during
-  // which HBM is idle; measured harmful (-2 % to -7 % per step) after HBM-bound kernels.
-  int l2_burst = 0;
   size_t smem_bytes = 0;
   int epilogue = kEpiStore;
   bool out_f32 = false;

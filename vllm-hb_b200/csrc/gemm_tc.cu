@@ -50,9 +50,6 @@ struct TcParams {
   int up_row_offset;        // SwiGLU: first row of the up projection inside W
   int cluster;              // split-K partners form a thread-block cluster of `splits` CTAs
   int tma_store;            // the output leaves through bulk tensor stores (tm_y is valid)
-  // k-chunks of this CTA's range requested into L2 before the dependency wait, beyond the
-  // ones that go straight to shared memory (see TcGemmPlan::l2_burst)
-  int l2_burst;
   // Deferred RMSNorm (see TcNormLink in gemm.h).  Producer (epilogue kEpiResidual, cluster
   // form only): h = resid + Y, written through tm_h; Y' = h * norm_w written through tm_y;
   // row sums of h^2 over this tile's 128 features to rowsq_out[row * rowsq_stride + tile].
@@ -280,13 +277,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         load_w(sa, kx, tile * kTileN, full);
         if (swiglu) load_w(sa + a_bytes, kx, p.up_row_offset + tile * kTileN, full);
       }
-      // ... and (l2_burst > 0) the chunks after them are requested into L2: for a GEMM whose
-      // predecessor leaves HBM idle (an exchange over NVLink).
-      for (int i = pre; i < min(n_kc, pre + p.l2_burst); ++i) {
-        const int kx = (kc0 + i) * kTileK;
-        tma_prefetch_2d(&tm_w, kx, tile * kTileN);
-        if (swiglu) tma_prefetch_2d(&tm_w, kx, p.up_row_offset + tile * kTileN);
-      }
+      // (Requesting further chunks into L2 at this point was measured harmful: -2 % to -7 % per
+      // decode step after HBM-bound kernels, no gain after an NVLink exchange.)
       pdl_wait();
       TC_LAUNCH_TRACE(3);
       for (int i = 0; i < pre; ++i) {
@@ -941,7 +933,6 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
                  pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
   pl.smem_bytes = pl.stages * stage + 1024;
-  pl.l2_burst = 0;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
   // partials where they expect zeroed counters.
@@ -1007,7 +998,6 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
   p.cluster = pl.cluster ? 1 : 0;
-  p.l2_burst = pl.l2_burst;
   CUtensorMap tm_y;
   memset(&tm_y, 0, sizeof(tm_y));
   const size_t y_elt = pl.out_f32 ? 4 : 2;

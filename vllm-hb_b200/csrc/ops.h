@@ -49,6 +49,10 @@ int fill_normal(cudaStream_t st, void* dst, hb_dtype dtype, int64_t rows, int64_
                 int64_t row0, int64_t col0, int64_t g_cols, uint64_t seed, uint64_t tensor_id,
                 float std, int64_t dst_ld = 0);  // dst_ld: row stride of dst in elements (0 = cols)
 int fill_const(cudaStream_t st, void* dst, hb_dtype dtype, int64_t n, float value);
+// dst [rows, cols] (row stride dst_ld elements, 0 = cols) := a dense [rows, cols] source of
+// another element type, converted on the device (round to nearest even).
+int convert_2d(cudaStream_t st, void* dst, hb_dtype dst_dtype, int64_t dst_ld, const void* src, hb_dtype src_dtype,
+               int64_t rows, int64_t cols);
 // dst (f32) = src (dtype)
 // cols / src_ld: the source is [n / cols, cols] with row stride src_ld (0 = contiguous)
 int to_f32(cudaStream_t st, float* dst, const void* src, hb_dtype dtype, int64_t n, int64_t cols = 0,

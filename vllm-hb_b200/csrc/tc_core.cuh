@@ -65,20 +65,9 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar), "l"(policy)
       : "memory");
 }
-// Asks the memory system to bring one box of the tensor map into L2; no shared memory, no
-// barrier, nothing to wait for.  Same 16-byte rule for x as the load.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tm, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tm), "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
 // Bulk tensor store shared -> global (box of the tensor map at element coordinates
