@@ -167,21 +167,24 @@ static int upload_slice(hb_engine* e, void* dst, const StTensor& t, int64_t cols
   const size_t src_es = t.dtype == "F32" ? 4 : 2;
   const uint8_t* src = t.data + ((size_t)r0 * cols + c0) * src_es;
   if (dst_ld <= 0) dst_ld = nc;
+  // every copy and conversion is ordered on the engine's stream; hb_engine_load synchronises it
+  // before the mapping goes away
   if (same_dtype(t.dtype, e->dtype)) {
-    HB_CUDA_CHECK(cudaMemcpy2D(dst, (size_t)dst_ld * e->es, src, (size_t)cols * src_es, (size_t)nc * src_es, (size_t)nr,
-                               cudaMemcpyHostToDevice));
+    HB_CUDA_CHECK(cudaMemcpy2DAsync(dst, (size_t)dst_ld * e->es, src, (size_t)cols * src_es, (size_t)nc * src_es,
+                                    (size_t)nr, cudaMemcpyHostToDevice, e->stream));
     return HB_OK;
   }
   const size_t need = (size_t)nr * nc * src_es;
   if (need > stage->bytes) {
+    HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));
     if (stage->buf) cudaFree(stage->buf);
     stage->buf = nullptr;
     stage->bytes = 0;
     HB_CUDA_CHECK(cudaMalloc(&stage->buf, need));
     stage->bytes = need;
   }
-  HB_CUDA_CHECK(cudaMemcpy2D(stage->buf, (size_t)nc * src_es, src, (size_t)cols * src_es, (size_t)nc * src_es, (size_t)nr,
-                             cudaMemcpyHostToDevice));
+  HB_CUDA_CHECK(cudaMemcpy2DAsync(stage->buf, (size_t)nc * src_es, src, (size_t)cols * src_es, (size_t)nc * src_es,
+                                  (size_t)nr, cudaMemcpyHostToDevice, e->stream));
   int rc = convert_2d(e->stream, dst, e->dtype, dst_ld, stage->buf, st_dtype(t.dtype), nr, nc);
   if (rc) return rc;
   HB_CUDA_CHECK(cudaStreamSynchronize(e->stream));  // the stage is reused by the next slice
@@ -1068,6 +1071,7 @@ int hb_engine_load(const hb_model_config* cfg, hb_world* world, hb_engine** out)
     if ((rc = get(pf + ".post_attention_layernorm.weight", 1, g->H, &t))) return rc;
     if ((rc = hb::upload_slice(g, w.norm_post, *t, g->H, 0, 1, 0, g->H, &scratch))) return rc;
   }
+  HB_CUDA_CHECK(cudaStreamSynchronize(g->stream));  // the mapped files are closed when this function returns
   if ((rc = hb::alloc_runtime(g, cfg))) return rc;
   *out = e.release();
   return HB_OK;
