@@ -503,7 +503,7 @@ int hb_kv_swap_blocks(hb_engine* e, const int64_t* pairs, size_t n_pairs, int to
 
 /* One decode step with CUDA events between its kernels — captured into a graph with an
  * event-record node after every kernel and replayed, so the kernels run back to back as in
- * a normal step (HB_PROFILE_EAGER=1 or HB_NO_GRAPH=1: issued kernel by kernel on the
+ * a normal step (HB_NO_GRAPH=1: issued kernel by kernel on the
  * stream): ms_by_kind receives HB_PROFILE_KINDS floats = device time spent in
  * 0 QKV projection, 1 decode attention, 2 RoPE + KV write, 3 (add +) RMSNorm, 4 embedding /
  * argmax / SwiGLU gate, 5 all-reduce, 6 o_proj, 7 gate|up projection, 8 down_proj,

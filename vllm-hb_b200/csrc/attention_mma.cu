@@ -420,12 +420,7 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
   const int64_t ctas = (int64_t)n_splits * hkv * n_seqs;
   // ... and a grid that does not even fill the SMs takes eight warps per CTA: two warps per
   // scheduler hide each other's MMA and softmax latency (70B TP=8 shape: 17.2 against 21.0 us)
-  int nw = ctas > 2 * (int64_t)di.sm_count ? 2 : (ctas <= (int64_t)di.sm_count ? 8 : 4);
-  if (const char* ev = getenv("HB_ATTN_WARPS")) {  // experiment knob
-    if (ev[0] == '2') nw = 2;
-    if (ev[0] == '4') nw = 4;
-    if (ev[0] == '8') nw = 8;  // one CTA per SM with two warps per scheduler: for grids below the SM count
-  }
+  const int nw = ctas > 2 * (int64_t)di.sm_count ? 2 : (ctas <= (int64_t)di.sm_count ? 8 : 4);
   if (nw == 8) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<8>, grid, dim3(256), mma_attn_smem(8), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,

@@ -372,7 +372,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // rows (accumulator columns) [r*CW, (r+1)*CW) of the tile for all 128 features;
     // everybody sends the columns it does not own to their owner, the owner adds the S
     // partials in split order (deterministic) and runs the epilogue for its rows.
-    // Both cluster barriers are reached unconditionally.
+    // Both cluster barriers are reached unconditionally.  (The same exchange through global
+    // scratch in L2 — plain stores by the partners, ld.global.cg by the owner, one cluster
+    // barrier less — was measured 0.5 to 2 us slower per launch on every decode shape.)
     const int S = p.splits, CW = p.m_pad / S;          // CW is a multiple of 4
     // receive area [S-1][n_acc][CW/4][128 features][4 columns] over the idle pipeline buffers
     float* recv = reinterpret_cast<float*>(smem_gen);
@@ -840,8 +842,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   pl.m_pad = (int)std::max<int64_t>(16, (m_eff + 15) / 16 * 16);
   pl.n_tiles = (int)((n_rows + kTileN - 1) / kTileN);
   const int k_chunks = (int)(K / kTileK);
-  const char* cl_env = getenv("HB_TC_CLUSTER");
-  const bool want_cluster = !(cl_env && cl_env[0] == '0');
+  const bool want_cluster = true;  // split-K partners reduce on chip; global scratch only where a cluster cannot form
   const bool tuned = want_cluster && force_splits <= 0 && g_plan_override[1] == 0 && g_plan_override[2] == 0;
   // Few weights under a wide batch (o_proj and q|k|v at high tensor-parallel degrees): the
   // split-K exchange moves 128 x m_pad fp32 per CTA through the SM-to-SM network, which at
