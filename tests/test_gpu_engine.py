@@ -331,6 +331,40 @@ def test_8b_widths_two_layers(hb, cuda):
     eng.close()
 
 
+@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (8, 1), (4, 4)], ids=["nrep4", "nrep8", "nrep1"])
+def test_prefill_chunks_share_the_kv_stream(hb, cuda, heads, kv_heads):
+    """A multi-token forward runs as chunks of consecutive positions; on the tensor-core
+    attention path 16 / n_rep of them share a CTA (each MMA row with its own causal limit,
+    src/engine/arch/llama_tp.rs:313-316).  The logits must equal those of feeding the same
+    tokens one at a time, and match the oracle's masked prefill."""
+    shape = dict(hidden_size=128 * heads, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=heads,
+                 num_key_value_heads=kv_heads, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=500000.0)
+    eng = hb.Engine.create_random(shape, seed=9, std=0.02, norm_ones=True, max_seq_len=128, bf16=True, max_batch=16)
+    cfg = R.LlamaTpConfig(**shape)
+    oracle = R.LlamaTpOracle(cfg, fetch_weights(eng, cfg), world_size=1, dtype="bf16", weights_exact=True)
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab_size, size=45).astype(np.uint32)   # chunks of 16, 16, 13
+    chunked = eng.create_kv_cache()
+    got = eng.forward_with_cache(prompt, 0, chunked)
+    one_by_one = eng.create_kv_cache()
+    for i, tok in enumerate(prompt):
+        ref = eng.forward_with_cache([int(tok)], i, one_by_one)
+    assert rel_err(got, ref) <= 2e-3          # same kernels, same order of the blocks per warp
+    want = oracle.forward(prompt.tolist(), 0, oracle.new_cache())
+    assert rel_err(got, want) <= 2e-2
+    # and the cache the chunks wrote serves a following decode step
+    tok = int(np.argmax(want))
+    assert rel_err(eng.forward_with_cache([tok], len(prompt), chunked),
+                   eng.forward_with_cache([tok], len(prompt), one_by_one)) <= 2e-3
+    # every position's logits (speculative verification) through the grouped kernel as well
+    seq3 = eng.create_kv_cache()
+    allpos = eng.forward_all_positions(prompt[:20], 0, seq3)
+    seq4 = eng.create_kv_cache()
+    for i in range(20):
+        ref_i = eng.forward_with_cache([int(prompt[i])], i, seq4)
+        assert rel_err(allpos[i], ref_i) <= 2e-3, i
+    eng.close()
+
+
 def test_step_bytes_formula(hb, cuda):
     eng = hb.Engine.create_random(SHAPE_TC, max_seq_len=64, bf16=True, max_batch=4)
     H, I, L, V, hd, hq, hkv = 512, 1024, 2, 2048, 64, 8, 2

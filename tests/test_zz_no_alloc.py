@@ -11,6 +11,8 @@ import numpy as np
 import pytest
 import torch
 
+from tests.test_gpu_kernels import oracle_attention
+
 pytestmark = pytest.mark.gpu
 
 
@@ -38,6 +40,11 @@ def test_static_scratch_matches_workspace_entry_point_twice(hb, cuda):
         err = float(np.max(np.abs(g_ - w))) / float(np.max(np.abs(w)))
         assert err <= 2e-2, (call, err)
         assert np.array_equal(g_, w), call
+        # ... and against the fp64 oracle of the attention tests, so that the two entry points
+        # cannot be wrong together
+        truth = oracle_attention(q.float().cpu().numpy(), kc.float().cpu().numpy(), vc.float().cpu().numpy(),
+                                 tables.cpu().numpy(), ctx.cpu().numpy(), kc.shape[1])
+        assert float(np.max(np.abs(g_ - truth))) / float(np.max(np.abs(truth))) <= 2e-2, call
 
 
 def test_static_scratch_single_split_and_size_limit(hb, cuda):

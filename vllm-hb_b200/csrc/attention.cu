@@ -317,7 +317,7 @@ bool paged_attention_mma_supported(const void* q, int64_t q_stride, const void* 
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh);
+                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh, int q_group);
 
 // Internal entry: q rows may sit inside a wider [q|k|v] projection buffer.  err_flag
 // (device int, may be null) is raised when a bounded wait of the tensor-core kernel ran out.
@@ -325,7 +325,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag, int window, int fresh_tokens) {
+                    hb_dtype dtype, int* err_flag, int window, int fresh_tokens, int q_group) {
   if (n_seqs == 0) return HB_OK;
   const int nrep = n_q_heads / n_kv_heads;
   float* po = (float*)workspace;
@@ -335,7 +335,7 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                                                    n_kv_heads, dtype)) {
     int rc = paged_attention_mma(st, out, po, pml, q, q_stride, k_cache, v_cache, block_tables, ctx_lens, n_seqs,
                                  n_q_heads, n_kv_heads, max_blocks_per_seq, num_blocks, n_splits, window, err_flag,
-                                 fresh_tokens);
+                                 fresh_tokens, q_group);
     if (rc) return rc;
     if (n_splits > 1) {
       attn_merge_kernel<__nv_bfloat16><<<(unsigned)(n_seqs * n_q_heads), 128, 0, st>>>(
@@ -383,7 +383,7 @@ int hb_paged_decode_attention(void* stream, void* out, const void* q, const void
   HB_CHECK_ARG(max_blocks_per_seq > 0 && num_blocks > 0, "hb_paged_decode_attention: bad block counts");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads,
-                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, 0, -1);
+                             head_dim, max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, 0, -1, 1);
 }
 
 int hb_paged_decode_attention_window(void* stream, void* out, const void* q, const void* k_cache,
@@ -404,7 +404,7 @@ int hb_paged_decode_attention_window(void* stream, void* out, const void* q, con
   HB_CHECK_ARG(sliding_window >= 0, "hb_paged_decode_attention_window: negative window");
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache,
                              v_cache, block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, sliding_window, -1);
+                             max_blocks_per_seq, num_blocks, n_splits, workspace, dtype, nullptr, sliding_window, -1, 1);
 }
 
 }  // extern "C"
@@ -469,7 +469,7 @@ int hb_paged_decode_attention_static(void* stream, void* out, const void* q, con
   if (rc) return rc;
   return hb::paged_attention((cudaStream_t)stream, out, q, (int64_t)n_q_heads * head_dim, k_cache, v_cache,
                              block_tables, ctx_lens, n_seqs, n_q_heads, n_kv_heads, head_dim,
-                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr, 0, -1);
+                             max_blocks_per_seq, num_blocks, n_splits, scratch, dtype, nullptr, 0, -1, 1);
 }
 
 }  // extern "C"

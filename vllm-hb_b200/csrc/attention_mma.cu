@@ -20,6 +20,11 @@
 //   At the end the warps merge their (m, l, O) through shared memory.
 //   When the caller bounds the tokens that the preceding kernels write (the engine's
 //   step), the ring is filled with older blocks before griddepcontrol.wait.
+//   Prefill chunks (q_group > 1): the rows of the batch are consecutive positions of ONE
+//   sequence; a CTA then takes q_group of them, the 16 MMA rows holding q_group positions x
+//   n_rep heads, each row with its own causal limit, so that the sequence's K and V are read
+//   once per q_group positions instead of once per position (src/engine/arch/llama_tp.rs:
+//   313-316: the causal mask of a multi-token forward).
 //
 // Every wait is bounded: on expiry the CTA raises *err_flag (when given), writes NaN
 // to its outputs, lets outstanding copies land and returns.
@@ -71,7 +76,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                       float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ q,
                       const int32_t* __restrict__ block_tables, const int32_t* __restrict__ ctx_lens, int hq,
                       int hkv, int nrep, int64_t max_blocks, int64_t num_blocks, int n_splits, float scale,
-                      int64_t q_stride, int window, int* err_flag, int fresh) {
+                      int64_t q_stride, int window, int* err_flag, int fresh, int q_group, int n_rows) {
   constexpr int kMmaAttnWarps = NW, kMmaAttnThreads = NW * 32;
   pdl_trigger();
   // fresh >= 0: at most `fresh` tokens at the end of every sequence were written by the
@@ -85,17 +90,26 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   __shared__ int s_abort;
 
   const int split = blockIdx.x, kvh = blockIdx.y;
-  const int64_t seq = blockIdx.z;
+  // the CTA's batch rows: [seq, seq + n_q); row seq + j holds position j of the group
+  const int64_t seq = (int64_t)blockIdx.z * q_group;
+  const int n_q = min(q_group, n_rows - (int)seq);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;  // MMA fragment coordinates
 
   // a context longer than the table row can describe is cut to the row (the table of the
   // next sequence, or memory past the allocation, is never indexed)
-  const int ctx = max(0, min(ctx_lens[seq], (int)min(max_blocks * HB_BLOCK_SIZE, (int64_t)INT_MAX)));
+  const int ctx_cap = (int)min(max_blocks * HB_BLOCK_SIZE, (int64_t)INT_MAX);
+  auto ctx_of = [&](int j) { return max(0, min(ctx_lens[seq + j], ctx_cap)); };
+  // MMA row r of the padded 16-row tile = (position r / nrep of the group, head r % nrep)
+  const int j_lo = g / nrep, j_hi = (g + 8) / nrep;
+  const bool row_lo = j_lo < n_q, row_hi = j_hi < n_q;
+  const int ctx_lo = row_lo ? ctx_of(j_lo) : 0, ctx_hi = row_hi ? ctx_of(j_hi) : 0;
+  const int ctx = ctx_of(n_q - 1);   // the longest context of the group (contexts grow with j)
   const int nblk = (ctx + HB_BLOCK_SIZE - 1) / HB_BLOCK_SIZE;
-  // sliding window (src/engine/arch/mixtral.rs:155-176): the query at position ctx-1 sees
-  // the keys ki with ctx-1-ki < window
-  const int first_tok = window > 0 ? max(0, ctx - window) : 0;
+  // sliding window (src/engine/arch/mixtral.rs:155-176): the query at position c-1 sees the
+  // keys ki with c-1-ki < window; the group's first row reaches furthest back
+  const int first_tok = window > 0 ? max(0, ctx_of(0) - window) : 0;
+  const int first_lo = window > 0 ? max(0, ctx_lo - window) : 0, first_hi = window > 0 ? max(0, ctx_hi - window) : 0;
   const int first_blk = first_tok / HB_BLOCK_SIZE;
   const int bps = (nblk - first_blk + n_splits - 1) / n_splits;
   const int b0 = first_blk + split * bps;
@@ -145,7 +159,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   int issued = 0;
   if (early) {
     // blocks [0, stable) were complete before this step began
-    const int stable = max(0, ctx - fresh) / HB_BLOCK_SIZE;
+    const int stable = max(0, ctx_of(0) - fresh) / HB_BLOCK_SIZE;
     for (; issued < min(kAttnStages, n_w); ++issued) {
       if (b0 + warp + kMmaAttnWarps * issued >= stable) break;
       issue(issued);
@@ -158,9 +172,9 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   // ---- query fragments: rows g and g+8 of the padded 16-head tile, all 8 k-steps
   uint32_t qa[8][4];
   {
-    const __nv_bfloat16* q0 = q + seq * q_stride + ((int64_t)kvh * nrep + g) * kAttnHD;
-    const __nv_bfloat16* q1 = q0 + 8 * kAttnHD;
-    const bool h0 = g < nrep, h1 = g + 8 < nrep;
+    const __nv_bfloat16* q0 = q + (seq + j_lo) * q_stride + ((int64_t)kvh * nrep + g % nrep) * kAttnHD;
+    const __nv_bfloat16* q1 = q + (seq + j_hi) * q_stride + ((int64_t)kvh * nrep + (g + 8) % nrep) * kAttnHD;
+    const bool h0 = row_lo, h1 = row_hi;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       const int col = ks * 16 + 2 * t;
@@ -224,7 +238,9 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int tok = tok0 + nt * 8 + 2 * t + (e & 1);
-        const float v = (tok < ctx && tok >= first_tok) ? sc[nt][e] * scale : -INFINITY;
+        // elements 0, 1 belong to row g, elements 2, 3 to row g + 8: each with its own limits
+        const bool vis = e < 2 ? (tok < ctx_lo && tok >= first_lo) : (tok < ctx_hi && tok >= first_hi);
+        const float v = vis ? sc[nt][e] * scale : -INFINITY;
         sc[nt][e] = v;
         if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
@@ -233,7 +249,9 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float m0n = fmaxf(m0, mx0), m1n = fmaxf(m1, mx1);  // finite: the block holds a valid token
+    // (a row of a group may see none of a block's tokens: its maximum then stays where it was,
+    // possibly still -inf, and the block adds nothing to it)
+    const float m0n = fmaxf(m0, mx0), m1n = fmaxf(m1, mx1);
     const float a0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - m0n);
     const float a1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - m1n);
     m0 = m0n; m1 = m1n;
@@ -248,8 +266,10 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       float p[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        p[nt][0] = __expf(sc[nt][0] - m0); p[nt][1] = __expf(sc[nt][1] - m0);
-        p[nt][2] = __expf(sc[nt][2] - m1); p[nt][3] = __expf(sc[nt][3] - m1);
+        p[nt][0] = sc[nt][0] == -INFINITY ? 0.f : __expf(sc[nt][0] - m0);
+        p[nt][1] = sc[nt][1] == -INFINITY ? 0.f : __expf(sc[nt][1] - m0);
+        p[nt][2] = sc[nt][2] == -INFINITY ? 0.f : __expf(sc[nt][2] - m1);
+        p[nt][3] = sc[nt][3] == -INFINITY ? 0.f : __expf(sc[nt][3] - m1);
         l0 += p[nt][0] + p[nt][1];
         l1 += p[nt][2] + p[nt][3];
       }
@@ -309,8 +329,8 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   __syncthreads();
   const bool failed = s_abort != 0;
   if (failed && tid == 0 && err_flag) atomicExch(err_flag, HB_ERR_TIMEOUT);
-  for (int idx = tid; idx < nrep * kAttnHD; idx += kMmaAttnThreads) {
-    const int h = idx / kAttnHD, d = idx % kAttnHD;
+  for (int idx = tid; idx < n_q * nrep * kAttnHD; idx += kMmaAttnThreads) {
+    const int h = idx / kAttnHD, d = idx % kAttnHD;   // h = MMA row = (position h / nrep, head h % nrep)
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kMmaAttnWarps; ++w) M = fmaxf(M, s_ml[(w * 16 + h) * 2]);
@@ -323,7 +343,7 @@ paged_attn_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       l += wt * s_ml[(w * 16 + h) * 2 + 1];
     }
     if (failed) { ov = __int_as_float(0x7fc00000); l = 1.f; }
-    const int64_t head = seq * hq + (int64_t)kvh * nrep + h;
+    const int64_t head = (seq + h / nrep) * hq + (int64_t)kvh * nrep + h % nrep;
     if (n_splits == 1) {
       out[head * kAttnHD + d] = __float2bfloat16_rn(l > 0.f ? ov / l : 0.f);
     } else {
@@ -402,13 +422,16 @@ int paged_attention_mma_prepare() {
 int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_ml, const void* q,
                         int64_t q_stride, const void* k_cache, const void* v_cache, const int32_t* block_tables,
                         const int32_t* ctx_lens, int64_t n_seqs, int hq, int hkv, int64_t max_blocks,
-                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh) {
+                        int64_t num_blocks, int n_splits, int window, int* err_flag, int fresh, int q_group) {
   int rc = paged_attention_mma_prepare();
+  const int nrep_ = hq / hkv;
+  if (q_group < 1 || q_group * nrep_ > 16) return fail(HB_ERR_INVALID_ARG, "paged attention: %d positions x %d heads exceed the 16 rows of a tile", q_group, nrep_);
+  const int n_rows = (int)n_seqs;
   if (rc) return rc;
   CUtensorMap tm_k, tm_v;
   if ((rc = encode_pool_map(&tm_k, k_cache, num_blocks, hkv))) return rc;
   if ((rc = encode_pool_map(&tm_v, v_cache, num_blocks, hkv))) return rc;
-  dim3 grid((unsigned)n_splits, (unsigned)hkv, (unsigned)n_seqs);
+  dim3 grid((unsigned)n_splits, (unsigned)hkv, (unsigned)((n_seqs + q_group - 1) / q_group));
   const float scale = 1.0f / sqrtf((float)kAttnHD);
   // Two CTAs of four warps fit an SM, or four of two warps (same bytes in flight).
   // When the grid is larger than one wave of the former, the smaller CTAs keep every
@@ -417,24 +440,24 @@ int paged_attention_mma(cudaStream_t st, void* out, float* part_o, float* part_m
   int device = 0;
   HB_CUDA_CHECK(cudaGetDevice(&device));
   if ((rc = device_info(device, &di))) return rc;
-  const int64_t ctas = (int64_t)n_splits * hkv * n_seqs;
+  const int64_t ctas = (int64_t)n_splits * hkv * ((n_seqs + q_group - 1) / q_group);
   // ... and a grid that does not even fill the SMs takes eight warps per CTA: two warps per
   // scheduler hide each other's MMA and softmax latency (70B TP=8 shape: 17.2 against 21.0 us)
   const int nw = ctas > 2 * (int64_t)di.sm_count ? 2 : (ctas <= (int64_t)di.sm_count ? 8 : 4);
   if (nw == 8) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<8>, grid, dim3(256), mma_attn_smem(8), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh, q_group, n_rows));
     return HB_OK;
   }
   if (nw == 2) {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<2>, grid, dim3(64), mma_attn_smem(2), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh, q_group, n_rows));
   } else {
     HB_CUDA_CHECK(launch_pdl(paged_attn_mma_kernel<4>, grid, dim3(128), mma_attn_smem(4), st, tm_k, tm_v,
                              (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, block_tables, ctx_lens, hq,
-                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh));
+                             hkv, hq / hkv, max_blocks, num_blocks, n_splits, scale, q_stride, window, err_flag, fresh, q_group, n_rows));
   }
   return HB_OK;
 }

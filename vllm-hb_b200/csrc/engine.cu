@@ -59,6 +59,7 @@ struct StepPlans {
   std::vector<TcGemmPlan> layer;  // [L * 4]
   TcGemmPlan lm_head;
   int attn_splits = 1;
+  int q_group = 1;          // prefill chunks: consecutive positions that share an attention CTA
   bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
   bool rope_epi = false;    // RoPE + KV write folded into the q|k|v GEMM epilogue (TcNormLink)
   bool push = false;        // o_proj / down_proj epilogues push their partials to the reducing ranks (kEpiPush)
@@ -375,11 +376,25 @@ static int pick_attn_splits(const hb_engine* e, int B) {
   return std::max(1, std::min(s, 16));
 }
 
-static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
-  auto it = e->plans.find(B);
+// Plans (and the captured graph) of a step of B rows; `chunk`: the rows are consecutive
+// positions of one sequence (a prefill chunk), which lets the attention kernel share the K/V
+// stream among them.
+static int ensure_plans(hb_engine* e, int B, bool chunk, StepPlans** out) {
+  const int key = B | (chunk ? 1 << 20 : 0);
+  auto it = e->plans.find(key);
   if (it != e->plans.end()) { *out = &it->second; return HB_OK; }
   StepPlans sp;
   sp.attn_splits = pick_attn_splits(e, B);
+  if (chunk && B > 1) {
+    const int nrep = (int)(e->hq_l / e->hkv_l);
+    const bool tc_attn = !getenv("HB_ATTN") &&
+                         paged_attention_mma_supported(e->d_qkv, e->qkv_rows, e->kc[0], e->vc[0], nrep, (int)e->hd,
+                                                       e->num_blocks, (int)e->hkv_l, e->dtype);
+    if (tc_attn && nrep <= 8) {
+      sp.q_group = 16 / nrep;   // 16 MMA rows = q_group positions x nrep heads
+      sp.attn_splits = 1;
+    }
+  }
   size_t ws = 0;
   if (e->use_tc) {
     sp.layer.resize(e->L * 4);
@@ -463,7 +478,7 @@ static int ensure_plans(hb_engine* e, int B, StepPlans** out) {
     for (auto& kv : e->plans)
       if (kv.second.graph) { cudaGraphExecDestroy(kv.second.graph); kv.second.graph = nullptr; }
   }
-  auto ins = e->plans.emplace(B, std::move(sp));
+  auto ins = e->plans.emplace(key, std::move(sp));
   *out = &ins.first->second;
   return HB_OK;
 }
@@ -593,7 +608,7 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     if ((rc = paged_attention(st, e->d_attn, e->d_qkv, e->qkv_rows, e->kc[l], e->vc[l], d_tables,
                               d_ctx, B, (int)e->hq_l, (int)e->hkv_l, (int)e->hd,
                               e->max_blocks_per_seq, e->num_blocks, sp->attn_splits, e->d_attn_ws,
-                              e->dtype, e->d_err, (int)e->window, attn_fresh))) return rc;
+                              e->dtype, e->d_err, (int)e->window, attn_fresh, sp->q_group))) return rc;
     e->last_launches += 1 + (sp->attn_splits > 1 ? 1 : 0);
     // o_proj partial, sum over ranks, residual, post-attention norm   llama_tp.rs:327,533-552
     prof_mark(e, kCatGemmO);
@@ -705,7 +720,7 @@ struct StepRow {
 };
 
 static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tokens, float* logits_out,
-                    int logits_row0);
+                    int logits_row0, bool chunk = false);
 
 static int decode_step(hb_engine* e, hb_seq* const* seqs, int B, const uint32_t* tokens,
                        uint32_t* next_tokens, float* logits_out /* host [B, V] or null */) {
@@ -741,8 +756,8 @@ static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float
     if ((rc = seq_ensure_block(e, s, s->len + c - 1))) return rc;
     for (int i = 0; i < c; ++i) rows[i] = {s->blocks.data(), s->blocks.size(), s->len + i, ids[done + i]};
     const bool last = done + (size_t)c == n;
-    if (all_positions) rc = run_rows(e, rows.data(), c, nullptr, logits_out + done * (size_t)e->V, 0);
-    else rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    if (all_positions) rc = run_rows(e, rows.data(), c, nullptr, logits_out + done * (size_t)e->V, 0, true);
+    else rc = run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1, true);
     if (rc) return rc;
     s->len += c;
     done += (size_t)c;
@@ -751,7 +766,7 @@ static int prefill(hb_engine* e, hb_seq* s, const uint32_t* ids, size_t n, float
 }
 
 static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tokens, float* logits_out,
-                    int logits_row0) {
+                    int logits_row0, bool chunk) {
   HB_CUDA_CHECK(cudaSetDevice(e->device));
   int rc;
   uint32_t* h_ids = (uint32_t*)(e->h_inputs + e->off_ids);
@@ -783,7 +798,7 @@ static int run_rows(hb_engine* e, const StepRow* rows, int B, uint32_t* next_tok
     for (int64_t i = 0; i < need; ++i) row[i] = (int32_t)r.blocks[i];
   }
   StepPlans* sp = nullptr;
-  if ((rc = ensure_plans(e, B, &sp))) return rc;
+  if ((rc = ensure_plans(e, B, chunk, &sp))) return rc;
   // only the used prefix of each region matters; one copy of the whole block is simplest
   HB_CUDA_CHECK(cudaMemcpyAsync(e->d_inputs, e->h_inputs, e->inputs_bytes, cudaMemcpyHostToDevice, e->stream));
   if (e->use_graph && !e->profiling) {
@@ -1274,7 +1289,7 @@ int hb_forward_tables(hb_engine* e, const uint32_t* ids, size_t n, size_t seq_po
     rows.resize((size_t)c);
     for (int i = 0; i < c; ++i) rows[i] = {block_table, table_len, (int64_t)(seq_pos + done) + i, ids[done + i]};
     const bool last = done + (size_t)c == n;
-    int rc = hb::run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1);
+    int rc = hb::run_rows(e, rows.data(), c, nullptr, last ? logits_out : nullptr, c - 1, true);
     if (rc) return rc;
     done += (size_t)c;
   }

@@ -810,14 +810,9 @@ static int pick_cluster_splits(int units, int k_chunks, int sm_count) {
   return s;
 }
 
-// Tuning hook (not part of the public interface): overrides the split factor, the pipeline
-// budget (1 = 200 KB / one CTA per SM, 2 = 110 KB) and the batch rows per tile of every
-// plan made afterwards; all zero restores the planner's own choice.
-static int g_plan_override[3] = {0, 0, 0};
-
 int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int64_t N, int64_t K,
                  int epilogue, bool out_f32, int device, int force_splits) {
-  if (g_plan_override[0] > 0) force_splits = g_plan_override[0];
+
   if (!gemm_tc_supported(M, N, K, HB_BF16))
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: unsupported shape M=%lld N=%lld K=%lld", (long long)M,
                 (long long)N, (long long)K);
@@ -837,13 +832,16 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   if (epilogue == kEpiSwiGLU && N % 2) return fail(HB_ERR_INVALID_ARG, "gemm_tc: SwiGLU needs even N");
   const int64_t n_rows = epilogue == kEpiSwiGLU ? N / 2 : N;  // output features
   pl.N = n_rows;
-  const int m_cap = n_acc == 2 ? 128 : 256;
+  // At most 128 batch rows per tile: a 256-row tile doubles the activation traffic per weight
+  // byte and the exchange per CTA (measured at M = 256: 8192 x 3584 38.0 -> 24.9 us, 8192 x 4096
+  // 40.7 -> 26.7 us with two tiles of 128 rows).
+  const int m_cap = 128;
   const int64_t m_eff = std::min<int64_t>(M, m_cap);
   pl.m_pad = (int)std::max<int64_t>(16, (m_eff + 15) / 16 * 16);
   pl.n_tiles = (int)((n_rows + kTileN - 1) / kTileN);
   const int k_chunks = (int)(K / kTileK);
   const bool want_cluster = true;  // split-K partners reduce on chip; global scratch only where a cluster cannot form
-  const bool tuned = want_cluster && force_splits <= 0 && g_plan_override[1] == 0 && g_plan_override[2] == 0;
+  const bool tuned = want_cluster && force_splits <= 0;
   // Few weights under a wide batch (o_proj and q|k|v at high tensor-parallel degrees): the
   // split-K exchange moves 128 x m_pad fp32 per CTA through the SM-to-SM network, which at
   // m_pad = 128 costs more than the matrix takes to stream.  Two batch tiles of 64 rows read
@@ -855,7 +853,6 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     pl.m_pad = 64;
     m_split = true;
   }
-  if (g_plan_override[2] > 0) pl.m_pad = std::min(pl.m_pad, std::max(16, g_plan_override[2] / 16 * 16));
   pl.m_tiles = (int)((M + pl.m_pad - 1) / pl.m_pad);
   const int units = pl.n_tiles * pl.m_tiles;
   const int acc_cols = pl.m_pad * n_acc;
@@ -870,7 +867,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   if ((size_t)small_stages * stage + 1024 > di.smem_optin)
     return fail(HB_ERR_INVALID_ARG, "gemm_tc: needs %zu bytes of shared memory", (size_t)small_stages * stage + 1024);
   const int slots = di.sm_count * 2;
-  bool big = g_plan_override[1] == 1;
+  bool big = false;
   if (force_splits > 0) {
     pl.splits = std::min(force_splits, k_chunks);
   } else if (!want_cluster) {
@@ -888,7 +885,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     int sp = 1;
     auto cta_bytes = [&](int s_) { return (size_t)(kTileN + pl.m_pad) * (size_t)(k_chunks / s_) * kTileK * 2; };
     while (sp < 8 && k_chunks / (sp * 2) >= 4 &&
-           (units * sp * 5 < di.sm_count * 4 || (cta_bytes(sp) > 512 * 1024 && units * sp < 2 * di.sm_count)))
+           (units * sp * 5 < di.sm_count * 4 || (cta_bytes(sp) > 512 * 1024 && units * sp < di.sm_count)))
       sp *= 2;
     pl.splits = sp;
   } else {
@@ -1095,12 +1092,6 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
 }
 
 }  // namespace hb
-
-extern "C" void hb_debug_gemm_override(int splits, int big, int m_pad) {
-  hb::g_plan_override[0] = splits;
-  hb::g_plan_override[1] = big;
-  hb::g_plan_override[2] = m_pad;
-}
 
 #ifdef HB_TC_TRACE
 extern "C" int hb_debug_tc_launches(unsigned long long* host_out, int n) {

@@ -9,7 +9,10 @@ int paged_attention(cudaStream_t st, void* out, const void* q, int64_t q_stride,
                     const void* v_cache, const int32_t* block_tables, const int32_t* ctx_lens,
                     int64_t n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
                     int64_t max_blocks_per_seq, int64_t num_blocks, int n_splits, void* workspace,
-                    hb_dtype dtype, int* err_flag = nullptr, int window = 0, int fresh_tokens = -1);
+                    hb_dtype dtype, int* err_flag = nullptr, int window = 0, int fresh_tokens = -1, int q_group = 1);
+// q_group > 1 (tensor-core kernel only): the rows are consecutive positions of ONE sequence
+// with the same block table (a prefill chunk); q_group of them share a CTA and the K/V stream.
+// Must satisfy q_group * (n_q_heads / n_kv_heads) <= 16 and needs n_splits == 1.
 // fresh_tokens >= 0: at most that many tokens at the end of every sequence were written by the
 // kernels launched right before this one; blocks of older tokens may be fetched before those
 // kernels have completed (programmatic launch).  -1: nothing is fetched early.
