@@ -3,6 +3,7 @@
     python vllm-hb_b200/bench_kernels.py gemm      [--cublas] [--iters 24] [--out FILE]
     python vllm-hb_b200/bench_kernels.py attention [--iters 24] [--out FILE]
     python vllm-hb_b200/bench_kernels.py gemm --only qkv8b --plain     # one shape, no graph: for ncu
+    python vllm-hb_b200/bench_kernels.py gemm --cublas --buffers 1     # weights resident in L2 where they fit
 
 gemm       Y = X W^T (hb_gemm_ex) on the projection shapes of the Llama-3.1-8B (TP=1) and
            70B (TP=2/4/8) decode steps, optionally next to torch.matmul (cuBLAS).
@@ -91,7 +92,7 @@ def bench_gemm(hb, args) -> list[dict]:
     for name, M, N, K, epi, f32 in GEMM_SHAPES:
         if args.only and name not in args.only.split(","):
             continue
-        nbuf = 3 if N * K * 2 > (256 << 20) else 6
+        nbuf = args.buffers or (3 if N * K * 2 > (256 << 20) else 6)
         iters = max(6, args.iters // 4) if N * K * 2 > (256 << 20) else args.iters
         g = torch.Generator(device=dev).manual_seed(1)
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
@@ -161,6 +162,9 @@ def main() -> None:
     ap.add_argument("--only", default="", help="comma-separated shape names")
     ap.add_argument("--cublas", action="store_true", help="gemm: also time torch.matmul on the same inputs")
     ap.add_argument("--plain", action="store_true", help="stream launches instead of a CUDA graph (for profilers)")
+    ap.add_argument("--buffers", type=int, default=0,
+                    help="gemm: weight buffers to rotate over (default 6, 3 for the largest; 1 keeps a matrix that "
+                         "fits in L2 resident there: the time that is left is the part of the kernel that is not HBM)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     hb = entry.load_package()

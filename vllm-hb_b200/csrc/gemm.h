@@ -79,6 +79,7 @@ struct TcGemmPlan {
   int n_tiles = 0;    // ceil(N / 128)
   int splits = 1;     // split-K factor
   bool cluster = false;  // the splits of a tile form a thread-block cluster (on-chip reduction)
+  bool recv_dedicated = false;  // cluster: the exchange's receive area lies behind the pipeline buffers
   int stages = 0;
   int tmem_cols = 0;
   size_t smem_bytes = 0;

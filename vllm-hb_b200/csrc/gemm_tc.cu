@@ -77,6 +77,7 @@ struct TcParams {
   int push_R, push_me, push_T;
   int64_t push_sv;
   uint32_t push_spin;
+  int recv_dedicated;       // cluster plans: the receive area of the exchange lies behind the pipeline buffers
   void* Y;
   float* partials;
   int* counters;
@@ -157,6 +158,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
   __shared__ __align__(8) uint64_t s_done;
+  __shared__ __align__(8) uint64_t s_recv;   // split-K exchange: bytes of the partners' partials landed
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_last;
@@ -193,6 +195,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     mbar_init(smem_u32(&s_done), 1);
     mbar_init(smem_u32(&s_resid), 1);
+    mbar_init(smem_u32(&s_recv), 1);
     s_abort = 0;
     s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -209,6 +212,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
+  if (p.cluster && p.splits > 1) {
+    // exchange barrier: armed with the bytes the S-1 partners will send.  With a dedicated
+    // receive area partners may send before this CTA is done streaming, so the cluster must
+    // know the barrier is initialised: everybody arrives here and waits just before the
+    // first remote store, by which time the barrier has long completed.
+    if (tid == 0)
+      mbar_expect_tx(smem_u32(&s_recv),
+                     (uint32_t)(p.splits - 1) * (uint32_t)(n_acc * (p.m_pad / p.splits) * kTileN * 4));
+    if (p.recv_dedicated) cluster_arrive_release();
+  }
   TC_TRACE(tid == 0, 1);
   pdl_launch_dependents();  // the next kernel may start its own prologue / weight prefetch
   if (!(warp == 0 && lane == 0)) pdl_wait();  // the producer waits after its weight prefetch
@@ -278,7 +291,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (swiglu) load_w(sa + a_bytes, kx, p.up_row_offset + tile * kTileN, full);
       }
       // (Requesting further chunks into L2 at this point was measured harmful: -2 % to -7 % per
-      // decode step after HBM-bound kernels, no gain after an NVLink exchange.)
+      // decode step after HBM-bound kernels, no gain after an NVLink exchange.  Requesting the
+      // NEXT kernel's weights into L2 once this CTA has issued its last load, so that HBM works
+      // through the tail: +0.1 to +0.4 % at 8-32 MB per launch, -1 % at 64 MB: the tail is not
+      // waiting for HBM.  With the weights already resident in L2 the 8B q|k|v projection takes
+      // 15.7 us instead of 17.6: the time is L2-to-SM transport and the serial chain of the tail.)
       pdl_wait();
       TC_LAUNCH_TRACE(3);
       for (int i = 0; i < pre; ++i) {
@@ -372,14 +389,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // rows (accumulator columns) [r*CW, (r+1)*CW) of the tile for all 128 features;
     // everybody sends the columns it does not own to their owner, the owner adds the S
     // partials in split order (deterministic) and runs the epilogue for its rows.
-    // Both cluster barriers are reached unconditionally.  (The same exchange through global
+    // The cluster barrier is reached unconditionally.  (The same exchange through global
     // scratch in L2 — plain stores by the partners, ld.global.cg by the owner, one cluster
     // barrier less — was measured 0.5 to 2 us slower per launch on every decode shape.)
     const int S = p.splits, CW = p.m_pad / S;          // CW is a multiple of 4
-    // receive area [S-1][n_acc][CW/4][128 features][4 columns] over the idle pipeline buffers
-    float* recv = reinterpret_cast<float*>(smem_gen);
+    // receive area [S-1][n_acc][CW/4][128 features][4 columns]: behind the pipeline buffers
+    // (dedicated: partners send as soon as THEIR accumulator is complete) or over them (a
+    // cluster barrier first tells everybody that all pipelines are idle); the staged output
+    // lies over the pipeline buffers either way
     const int slot_floats = n_acc * CW * kTileN;
-    const uint32_t out_off = (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
+    const uint32_t recv_off = p.recv_dedicated ? (uint32_t)p.stages * stage_bytes : 0u;
+    float* recv = reinterpret_cast<float*>(smem_gen + recv_off);
+    const uint32_t out_off = p.recv_dedicated ? 0u : (uint32_t)((S - 1) * slot_floats) * 4u;  // staged output [CW][128]
     const bool residual = p.epilogue == kEpiResidual;
     const uint32_t tile_b = (uint32_t)CW * kTileN * 2u;   // one staged bf16 tile
     const uint32_t h_off = out_off + tile_b;              // kEpiResidual: new residual [CW][128]
@@ -391,9 +412,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_expect_tx(bar, tile_b);
       tma_load_2d(smem_base + resid_off, &tm_h, tile * kTileN, m_base + split * CW, bar);
     }
-    cluster_sync_all();  // every partner's pipeline buffers are idle from here on
+    if (p.recv_dedicated) cluster_wait_acquire();  // every partner's exchange barrier is initialised
+    else cluster_sync_all();                       // every partner's pipeline buffers are idle from here on
     TC_TRACE(tid == 0, 5);
     if (ok_all) {
+      const uint32_t bar_local = smem_u32(&s_recv);
       for (int acc = 0; acc < n_acc; ++acc) {
         for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
           // groups this CTA owns entirely stay in tensor memory (uniform over the CTA)
@@ -407,19 +430,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (owner != split) {
               const int slot = split < owner ? split : split - 1;
               const uint32_t local =
-                  smem_base +
+                  smem_base + recv_off +
                   (uint32_t)(slot * slot_floats + ((acc * (CW >> 2) + ((c % CW) >> 2)) * kTileN + row) * 4) * 4u;
-              st_cluster_v4(cluster_map(local, (uint32_t)owner), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              st_async_v4(cluster_map(local, (uint32_t)owner), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3],
+                          cluster_map(bar_local, (uint32_t)owner));
             }
           }
         }
       }
     }
-    cluster_sync_all();  // release/acquire: the columns sent above are visible to their owner
+    // the partners' columns: every 16-byte store above reports to its owner's barrier, which
+    // completes when all (S-1) partial slices have landed.  No CTA leaves before it has
+    // received everything addressed to it, so no store can arrive at a CTA that has exited.
+    const bool ok_recv = ok_all && mbar_wait(smem_u32(&s_recv), 0, &s_abort);
     TC_TRACE(tid == 0, 6);
     bool resid_ok = true;
     const float w_norm = (residual && n_glob < p.N) ? __bfloat162float(p.norm_w[n_glob]) : 0.f;
-    if (ok_all) {
+    if (ok_recv) {
       const int c_lo = split * CW;
       for (int c0 = c_lo & ~15; c0 < c_lo + CW; c0 += 16) {
         float own[16], own_u[16], g[16], u[16];
@@ -501,7 +528,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       fence_async_smem();
     }
     TC_TRACE(tid == 0, 10);
-    const bool tail_ok = __syncthreads_and((ok_all && resid_ok) ? 1 : 0) != 0;
+    const bool tail_ok = __syncthreads_and((ok_recv && resid_ok) ? 1 : 0) != 0;
     TC_TRACE(tid == 0, 11);
     if (tail_ok && residual) {
       // sum of squares of every new residual row over this tile's 128 features: a warp per
@@ -930,7 +957,27 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     pl.cluster = pl.splits > 1 && pl.splits <= 8 && (pl.splits & (pl.splits - 1)) == 0 &&
                  pl.m_pad % (4 * pl.splits) == 0 && recv_fits(pl.splits);
   }
-  pl.smem_bytes = pl.stages * stage + 1024;
+  // Where the budget leaves at least three stages beside it, the receive area of the exchange
+  // gets shared memory of its own behind the pipeline: partners then send without waiting for
+  // this CTA's pipeline to drain (one cluster barrier less in the tail).
+  pl.recv_dedicated = false;
+  size_t recv_bytes = 0;
+  if (pl.cluster) {
+    const size_t cw = (size_t)pl.m_pad / pl.splits;
+    recv_bytes = (size_t)(pl.splits - 1) * n_acc * cw * kTileN * sizeof(float);
+    const size_t staged = cw * kTileN * out_elt + (epilogue == kEpiResidual ? 2 * cw * kTileN * 2 : 0);
+    const size_t budget = (pl.stages == big_stages && big_stages > small_stages) ? big_budget : small_budget;
+    const int st_d = budget > recv_bytes ? (int)std::min<size_t>(kMaxStages, (budget - recv_bytes) / stage) : 0;
+    static const int mode = [] { const char* v = getenv("HB_TC_RECV"); return v ? atoi(v) : -1; }();
+    const int min_stages = mode == 1 ? 2 : 3;
+    if (mode != 0 && st_d >= min_stages && staged <= (size_t)st_d * stage) {
+      pl.recv_dedicated = true;
+      pl.stages = st_d;
+    } else {
+      recv_bytes = 0;
+    }
+  }
+  pl.smem_bytes = pl.stages * stage + recv_bytes + 1024;
   // The tile counters sit in a block of FIXED size at the start of the workspace, so
   // that plans of different shapes sharing one workspace never see each other's
   // partials where they expect zeroed counters.
@@ -996,6 +1043,7 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
   p.partials = workspace ? (float*)((uint8_t*)workspace + pl.ws_counters_bytes) : nullptr;
   p.err_flag = err_flag;
   p.cluster = pl.cluster ? 1 : 0;
+  p.recv_dedicated = pl.recv_dedicated ? 1 : 0;
   CUtensorMap tm_y;
   memset(&tm_y, 0, sizeof(tm_y));
   const size_t y_elt = pl.out_f32 ? 4 : 2;

@@ -164,6 +164,20 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t caddr, float a, float b, 
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+// 16-byte store into a partner CTA's shared memory that reports its bytes to an mbarrier of
+// THAT CTA (both addresses already mapped into the partner's window): the receiver waits on
+// its own barrier and needs no cluster-wide barrier or fence to see the data.
+__device__ __forceinline__ void st_async_v4(uint32_t caddr, float a, float b, float c, float d, uint32_t cbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(caddr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(cbar)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 // Every thread of every CTA of the cluster arrives; hardware barrier, always reached.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
