@@ -293,8 +293,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // (Requesting further chunks into L2 at this point was measured harmful: -2 % to -7 % per
       // decode step after HBM-bound kernels, no gain after an NVLink exchange.  Requesting the
       // NEXT kernel's weights into L2 once this CTA has issued its last load, so that HBM works
-      // through the tail: +0.1 to +0.4 % at 8-32 MB per launch, -1 % at 64 MB: the tail is not
-      // waiting for HBM.  With the weights already resident in L2 the 8B q|k|v projection takes
+      // through the tail (a linear prefix of 8-32 MB, or per CTA of the next kernel the 1-4
+      // chunks after the stages it fetches by itself): within +-0.4 % per step, -1.5 % and worse
+      // from 8 chunks or 64 MB: neither the tail nor the restart of the stream waits for HBM.  With the weights already resident in L2 the 8B q|k|v projection takes
       // 15.7 us instead of 17.6: the time is L2-to-SM transport and the serial chain of the tail.)
       pdl_wait();
       TC_LAUNCH_TRACE(3);
@@ -452,6 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         float own[16], own_u[16], g[16], u[16];
         tmem_ld16(t_lane + c0, own);
         if (swiglu) tmem_ld16(t_lane + p.m_pad + c0, own_u);
+        TC_TRACE(tid == 0 && c0 == (c_lo & ~15), 13);
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
         // partials are added in split order (deterministic); the 16 columns are
@@ -480,6 +482,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             }
           }
         }
+        TC_TRACE(tid == 0 && c0 == (c_lo & ~15), 14);
+        // (Requesting all partners' pieces of a four-column group before the first addition, and
+        // two tensor-memory loads per wait in the send loop, took the kernel from 96 to 178
+        // registers and made it SLOWER: q|k|v of the 8B shape 16.5 -> 17.5 us.)
         if (p.rowsq_in) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
