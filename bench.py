@@ -421,6 +421,12 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     if world > 1:
         staging = 64 << 20
         tp_world = hb.TpWorld.from_torch_distributed(local_rank, staging_bytes=staging, nccl=True)
+        # the exchange after o_proj / down_proj: sum formed inside the NVLink switch where the
+        # fabric offers multicast, else the peer-memory kernel
+        exchange = "peer memory (--exchange peer)"
+        if args.exchange == "auto":
+            why = tp_world.enable_multicast(256, max(8192, shape["hidden_size"]))
+            exchange = "switch reduction (multimem)" if not why else f"peer memory ({why})"
         if args.workload == "auto" and not args.skip_checks:
             # correctness on all N ranks first (untimed); a failure ends the run non-zero
             parity = tp_parity(hb, tp_world, rank, world, dev)
@@ -515,7 +521,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": gpu_config(w, world, K),
+            "config": dict(gpu_config(w, world, K), **({"exchange": exchange} if world > 1 else {})),
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B + 4},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel (all GEMM launches of a step)",
@@ -546,6 +552,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     eng.close()
     if tp_world is not None:
         barrier()
+        tp_world.disable_multicast()  # collective; before the window's memory and the process group go away
         tp_world.close()
     if world > 1:
         dist.destroy_process_group()
@@ -565,6 +572,9 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--profile-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["auto", "peer"], default="auto",
+                    help="N > 1: 'auto' reduces inside the NVLink switch when multicast memory is available, 'peer' "
+                         "always takes the peer-memory kernel")
     ap.add_argument("--skip-checks", action="store_true",
                     help="N > 1: skip the untimed parity checks, the single-GPU base point and the row-parallel points")
     ap.add_argument("--tp1-layers", type=int, default=8, help="layers of the single-GPU base point of the N > 1 shape")

@@ -48,7 +48,9 @@ typedef enum hb_algo {
   HB_ALGO_AUTO = 0,     /* one-shot below the crossover size, two-shot above */
   HB_ALGO_ONE_SHOT = 1, /* every rank reads all partials: (R-1)*bytes inbound, one flag hop */
   HB_ALGO_TWO_SHOT = 2, /* reduce-scatter + all-gather: 2(R-1)/R*bytes, two flag hops */
-  HB_ALGO_NCCL = 3      /* ncclAllReduce: the reference's path, kept as the reported baseline */
+  HB_ALGO_NCCL = 3,     /* ncclAllReduce: the reference's path, kept as the reported baseline */
+  HB_ALGO_MULTIMEM = 4  /* hb_all_reduce_add_rms_norm / hb_fused_rowparallel only: the sum is formed
+                           inside the NVLink switch (needs hb_world_attach_multicast) */
 } hb_algo;
 
 const char* hb_last_error(void);
@@ -254,6 +256,24 @@ int hb_world_attach(hb_world* w, const void* all_handles);
  * elsewhere (for example a symmetric-memory allocation); peer_ptrs[rank] is this
  * rank's own buffer of at least hb_world_staging_bytes(). */
 int hb_world_attach_ptrs(hb_world* w, void* const* peer_ptrs);
+/* Optional window for HB_ALGO_MULTIMEM (reduction inside the NVLink switch, NVLink SHARP).
+ * The caller allocates hb_world_multicast_bytes(max_rows, hidden) bytes on every rank, binds
+ * the R allocations to ONE multicast object (cuMulticastCreate / cuMulticastAddDevice /
+ * cuMulticastBindMem + cuMemMap, or a framework's symmetric-memory allocator that does the
+ * same) and passes this rank's ordinary address of its allocation and the multicast address.
+ * The library zeroes the window's first 64 KiB; all ranks attach, THEN synchronise on the
+ * host, then use it.  The memory stays the caller's: detach (which drains the device) before
+ * unbinding or freeing it, on every rank, and end no process while its window is bound.
+ * After HB_ERR_TIMEOUT in a call that used the window its counters are out of step: detach
+ * and attach again on all ranks.  bf16 rows only, world sizes 2, 4 and 8, hidden a multiple
+ * of 8 * world_size, at most 256 rows.  hb_world_multicast_partial: the address inside the window where a
+ * row-parallel GEMM should leave its [rows, hidden] partial; hb_all_reduce_add_rms_norm
+ * copies a partial that lies elsewhere. */
+size_t hb_world_multicast_bytes(int64_t max_rows, int64_t hidden);
+int hb_world_attach_multicast(hb_world* w, void* local_ptr, void* multicast_ptr, size_t bytes);
+int hb_world_detach_multicast(hb_world* w);
+int hb_world_has_multicast(const hb_world* w);
+void* hb_world_multicast_partial(const hb_world* w);
 /* Optional NCCL communicator for HB_ALGO_NCCL: unique id from hb_nccl_unique_id on
  * rank 0, passed to every rank. */
 #define HB_NCCL_ID_BYTES 128
@@ -318,13 +338,20 @@ int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void
  *   HB_ROWPAR_EXCHANGE  GEMM to a local partial, then hb_all_reduce_add_rms_norm
  *                       (HB_ALGO_ONE_SHOT, small messages, shapes the push form cannot take);
  *   HB_ROWPAR_NCCL      GEMM -> ncclAllReduce -> add + RMSNorm, the reference's own sequence
- *                       (HB_ALGO_NCCL; needs hb_world_init_nccl): the reported baseline.
+ *                       (HB_ALGO_NCCL; needs hb_world_init_nccl): the reported baseline;
+ *   HB_ROWPAR_MULTIMEM  the GEMM writes its partial into the world's multicast window, one
+ *                       kernel per rank lets the NVLink switch form the sum (one load that
+ *                       returns the sum over all ranks, one store that reaches all ranks),
+ *                       adds the residual and normalises (HB_ALGO_MULTIMEM; needs
+ *                       hb_world_attach_multicast).  Sums agree with the other forms to
+ *                       bf16 rounding (the switch's order of addition is its own).
  * Shapes none of the forms covers fail with HB_ERR_INVALID_ARG.
  * norm_w may be NULL (then normed_out is not written). */
 #define HB_ROWPAR_SINGLE 0
 #define HB_ROWPAR_PUSH 1
 #define HB_ROWPAR_EXCHANGE 2
 #define HB_ROWPAR_NCCL 3
+#define HB_ROWPAR_MULTIMEM 4
 int hb_fused_rowparallel_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_algo algo);
 size_t hb_fused_rowparallel_workspace_bytes(int64_t M, int64_t N, int64_t K_local);
 int hb_fused_rowparallel(hb_world* w, void* stream, void* normed_out, void* resid_out,

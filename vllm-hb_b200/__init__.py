@@ -35,7 +35,7 @@ if not LIB_PATH.exists():
 lib = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
 
 F32, F16, BF16 = 0, 1, 2
-ALGO_AUTO, ALGO_ONE_SHOT, ALGO_TWO_SHOT, ALGO_NCCL = 0, 1, 2, 3
+ALGO_AUTO, ALGO_ONE_SHOT, ALGO_TWO_SHOT, ALGO_NCCL, ALGO_MULTIMEM = 0, 1, 2, 3, 4
 BLOCK_SIZE = 16
 IPC_HANDLE_BYTES = 64
 NCCL_ID_BYTES = 128
@@ -124,6 +124,11 @@ _SIGS = {
     "hb_world_stream": (_vp, [_vp]),
     "hb_world_status": (_i, [_vp]),
     "hb_world_set_wait_limit": (_i, [_vp, C.c_uint32]),
+    "hb_world_multicast_bytes": (C.c_size_t, [_i64, _i64]),
+    "hb_world_attach_multicast": (_i, [_vp, _vp, _vp, C.c_size_t]),
+    "hb_world_detach_multicast": (_i, [_vp]),
+    "hb_world_has_multicast": (_i, [_vp]),
+    "hb_world_multicast_partial": (_vp, [_vp]),
     "hb_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i]),
     "hb_all_reduce_add_rms_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i]),
     "hb_fused_rowparallel_workspace_bytes": (_sz, [_i64, _i64, _i64]),
@@ -546,6 +551,69 @@ class TpWorld:
         """Polls after which a device-side wait on a peer flag gives up (0 = default)."""
         check(lib.hb_world_set_wait_limit(self.handle, polls))
 
+    def enable_multicast(self, max_rows: int, hidden: int, group=None) -> str:
+        """Gives the world a window for ALGO_MULTIMEM (the sum formed inside the NVLink switch).
+        Collective over `group` (default: all ranks).  The window comes from torch's
+        symmetric-memory allocator, which binds the ranks' allocations to one multicast
+        object; returns "" on success, else why the switch reduction is unavailable (every
+        rank gets the same answer).  Call disable_multicast() on every rank before the
+        process group goes away."""
+        import torch
+        import torch.distributed as dist
+
+        why = ""
+        tensor = handle = None
+        nbytes = lib.hb_world_multicast_bytes(max_rows, hidden)
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            dev = torch.device("cuda", self.device())
+            grp = group if group is not None else dist.group.WORLD
+            tensor = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+            handle = symm.rendezvous(tensor, grp)
+            if not int(handle.multicast_ptr):
+                why = "the symmetric-memory allocation has no multicast address (no NVLink switch reduction here)"
+        except Exception as exc:  # allocator or rendezvous not available in this build / on this fabric
+            why = f"symmetric memory unavailable: {type(exc).__name__}: {exc}"
+        # every rank must agree before anybody starts to use the window
+        flags: list = [None] * dist.get_world_size(group)
+        dist.all_gather_object(flags, why, group=group)
+        bad = [f for f in flags if f]
+        if bad:
+            return bad[0]
+        check(lib.hb_world_attach_multicast(self.handle, tensor.data_ptr(), int(handle.multicast_ptr), nbytes))
+        self._mc = (tensor, handle, group)
+        # a rank that leaves on an error still unbinds its memory before the process ends
+        import atexit
+
+        atexit.register(self.close)
+        dist.barrier(group=group)
+        return ""
+
+    def has_multicast(self) -> bool:
+        return bool(lib.hb_world_has_multicast(self.handle))
+
+    def multicast_partial(self, rows: int, hidden: int, dtype):
+        """The [rows, hidden] view inside the window where a row-parallel GEMM leaves its partial."""
+        tensor = self._mc[0]
+        off = lib.hb_world_multicast_partial(self.handle) - tensor.data_ptr()
+        return tensor[off:off + rows * hidden * 2].view(dtype).view(rows, hidden)
+
+    def disable_multicast(self, collective: bool = True) -> None:
+        """Drains the device, forgets the window and releases it.  collective=True (the normal
+        path): all ranks do so together, between barriers.  collective=False is for a rank that
+        is about to leave on an error: it still unbinds its own memory before the process ends."""
+        import torch.distributed as dist
+
+        mc = getattr(self, "_mc", None)
+        if mc is None:
+            return
+        check(lib.hb_world_detach_multicast(self.handle))
+        if collective:
+            dist.barrier(group=mc[2])
+        self._mc = None
+        del mc
+
     def all_reduce(self, buf, algo: int = ALGO_AUTO, stream=None):
         """In-place SUM over ranks of a torch CUDA tensor (TpWorld::all_reduce)."""
         check(lib.hb_all_reduce(self.handle, _stream(stream), _ptr(buf), buf.numel(),
@@ -568,6 +636,8 @@ class TpWorld:
         return fused_rowparallel(self, x, w, resid, norm_w, eps, algo, stream)
 
     def close(self) -> None:
+        if self.handle and getattr(self, "_mc", None) is not None:
+            self.disable_multicast(collective=False)
         if self.handle and self._owner:
             lib.hb_world_free(self.handle)
         self.handle = None
@@ -606,7 +676,7 @@ def fused_rowparallel(world, x, w, resid, norm_w, eps: float, algo: int = ALGO_A
     return normed, res
 
 
-ROWPAR_FORMS = {0: "single", 1: "push", 2: "exchange", 3: "nccl"}
+ROWPAR_FORMS = {0: "single", 1: "push", 2: "exchange", 3: "nccl", 4: "multimem"}
 
 
 def fused_rowparallel_form(world, M: int, N: int, K_local: int, algo: int = ALGO_AUTO) -> str:

@@ -39,6 +39,8 @@ def run_points(hb, tp, rank: int, world: int, dev, hbm_gbs: float, ms=(1, 8, 64,
 
     rows = []
     side = torch.cuda.Stream(device=dev)
+    # the fused arm takes the switch reduction where the world has a multicast window
+    algo = hb.ALGO_MULTIMEM if tp is not None and tp.has_multicast() else hb.ALGO_AUTO
     for K, N in shapes:
         Kl = K // world
         w_bytes = N * Kl * 2
@@ -56,7 +58,7 @@ def run_points(hb, tp, rank: int, world: int, dev, hbm_gbs: float, ms=(1, 8, 64,
             part = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
 
             def fused(i):
-                hb.fused_rowparallel(tp, x, ws[i], resid, nw, 1e-5, hb.ALGO_AUTO, workspace=fws, out=out_f)
+                hb.fused_rowparallel(tp, x, ws[i], resid, nw, 1e-5, algo, workspace=fws, out=out_f)
 
             def baseline(i):
                 st = torch.cuda.current_stream().cuda_stream
@@ -94,7 +96,7 @@ def run_points(hb, tp, rank: int, world: int, dev, hbm_gbs: float, ms=(1, 8, 64,
                 del graph
                 return float(t)
 
-            row = {"M": M, "K": K, "N": N, "tp": world, "form": hb.fused_rowparallel_form(tp, M, N, Kl, hb.ALGO_AUTO),
+            row = {"M": M, "K": K, "N": N, "tp": world, "form": hb.fused_rowparallel_form(tp, M, N, Kl, algo),
                    "weight_sets": n_sets, "calls_per_graph": calls}
             row["fused_us"] = graph_time(fused)
             row["baseline_us"] = graph_time(baseline)

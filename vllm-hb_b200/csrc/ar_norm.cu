@@ -336,6 +336,10 @@ bool ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dty
 int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
                       const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
                       hb_dtype dtype, hb_algo algo, const PushGeometry* staged) {
+  if (algo == HB_ALGO_MULTIMEM) {
+    if (staged) return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: the switch reduction takes no pushed partials");
+    return world_mm_ar_add_norm(w, st, normed_out, resid_out, partial, resid_in, norm_w, M, N, eps, dtype);
+  }
   if (!ar_add_norm_supported(w, M, N, dtype))
     return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: unsupported shape %lld x %lld or world", (long long)M,
                 (long long)N);

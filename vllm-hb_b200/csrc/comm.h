@@ -31,6 +31,14 @@ struct CommFlags {
 };
 static_assert(sizeof(CommFlags) <= kFlagBytes, "flag block too large");
 
+// The same operation with the sum done inside the NVLink switch (ar_multimem.cu); needs a
+// multicast window.  mm_partial_ptr: where inside the window a GEMM leaves its partial so that
+// nothing has to be copied.
+bool mm_ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
+void* mm_partial_ptr(const hb_world* w);
+int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
+                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype);
+
 }  // namespace hb
 
 struct hb_world {
@@ -43,6 +51,11 @@ struct hb_world {
   bool owns_local = true;
   bool attached = false;
   void* nccl = nullptr;               // ncclComm_t when hb_world_init_nccl ran
+  // window mapped into a multicast object by the caller (hb_world_attach_multicast): this rank's
+  // ordinary address, the multicast address, size
+  void* mc_local = nullptr;
+  void* mc_base = nullptr;
+  size_t mc_bytes = 0;
   uint32_t wait_limit = 1u << 22;     // polls before a device-side wait on a peer flag gives up
   int32_t* host_status = nullptr;     // pinned mirror for hb_world_status
 };
@@ -68,5 +81,13 @@ bool push_exchange_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype d
 int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
                       const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
                       hb_dtype dtype, hb_algo algo, const PushGeometry* staged = nullptr);
+
+// The same operation with the sum done inside the NVLink switch (ar_multimem.cu); needs a
+// multicast window.  mm_partial_ptr: where inside the window a GEMM leaves its partial so that
+// nothing has to be copied.
+bool mm_ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
+void* mm_partial_ptr(const hb_world* w);
+int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
+                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype);
 
 }  // namespace hb

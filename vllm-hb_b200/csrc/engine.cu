@@ -61,6 +61,7 @@ struct StepPlans {
   int attn_splits = 1;
   int q_group = 1;          // prefill chunks: consecutive positions that share an attention CTA
   bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
+  bool mm = false;          // exchange through the NVLink switch (multicast window of the world)
   bool rope_epi = false;    // RoPE + KV write folded into the q|k|v GEMM epilogue (TcNormLink)
   bool push = false;        // o_proj / down_proj epilogues push their partials to the reducing ranks (kEpiPush)
   PushGeometry geo_o, geo_down;
@@ -414,11 +415,14 @@ static int ensure_plans(hb_engine* e, int B, bool chunk, StepPlans** out) {
     // reducing ranks' staging (the first hop of the all-reduce rides in the GEMM epilogue)
     // when the batch is large enough for the two-hop exchange (HB_PUSH=0: GEMM, then the
     // exchange kernel reads the partial back; HB_PUSH=1: push at every batch size).
+    // A world with a multicast window lets the switch form the sum instead (HB_MULTIMEM=0: not).
     {
+      static const bool mm_off = [] { const char* v = getenv("HB_MULTIMEM"); return v && v[0] == '0'; }();
+      sp.mm = e->ws > 1 && !mm_off && mm_ar_add_norm_supported(e->world, B, e->H, e->dtype);
       const char* pe = getenv("HB_PUSH");
       const bool off = pe && pe[0] == '0', always = pe && pe[0] == '1';
       const bool two_hop = e->ws > 2 && (size_t)B * e->H * e->es > 128 * 1024;
-      sp.push = e->ws > 1 && !off && (always || two_hop) && push_exchange_supported(e->world, B, e->H, e->dtype);
+      sp.push = e->ws > 1 && !sp.mm && !off && (always || two_hop) && push_exchange_supported(e->world, B, e->H, e->dtype);
       if (sp.push) {
         TcGemmPlan probe_o, probe_d;
         auto& w0 = e->layers[0];
@@ -512,12 +516,19 @@ static void prof_mark(hb_engine* e, int cat) {
 
 // h += SUM_ranks d_proj; x = norm(h; norm_w): one kernel over peer memory when the world has
 // several ranks (shapes the kernel does not take: all-reduce kernel, then add+norm), add+norm alone otherwise.
-static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B) {
+static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B, bool mm = false) {
   int rc;
   cudaStream_t st = e->stream;
   const float eps = (float)e->eps;
   if (e->ws > 1) {
     prof_mark(e, kCatComm);
+    if (mm) {
+      // the projection left its partial in the world's multicast window: the switch sums it
+      if ((rc = world_mm_ar_add_norm(e->world, st, x_out, e->d_h, mm_partial_ptr(e->world), e->d_h, norm_w, B, e->H, eps,
+                                     e->dtype))) return rc;
+      ++e->last_launches;
+      return HB_OK;
+    }
     if (ar_add_norm_supported(e->world, B, e->H, e->dtype)) {
       if ((rc = world_ar_add_norm(e->world, st, x_out, e->d_h, e->d_proj, e->d_h, norm_w, B, e->H, eps, e->dtype,
                                   HB_ALGO_AUTO))) return rc;
@@ -627,8 +638,9 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       produce.rowsq_stride = e->rowsq_stride;
       if ((rc = run_gemm(e, sp, l, kO, e->d_x, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false, &produce))) return rc;
     } else {
-      if ((rc = run_gemm(e, sp, l, kO, e->d_proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
-      if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B))) return rc;
+      void* proj = sp->mm ? mm_partial_ptr(e->world) : e->d_proj;
+      if ((rc = run_gemm(e, sp, l, kO, proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
+      if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B, sp->mm))) return rc;
     }
     // mixture of experts: routing weights of every token       mixtral.rs:371-412
     if (e->moe) {
@@ -680,8 +692,9 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       produce.rowsq_stride = e->rowsq_stride;
       if ((rc = run_gemm(e, sp, l, kDown, e->d_x, e->d_act, w.wdown, B, e->H, e->I_e, false, &produce))) return rc;
     } else {
-      if ((rc = run_gemm(e, sp, l, kDown, e->d_proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
-      if ((rc = reduce_add_norm(e, e->d_x, nw, B))) return rc;
+      void* proj = sp->mm ? mm_partial_ptr(e->world) : e->d_proj;
+      if ((rc = run_gemm(e, sp, l, kDown, proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
+      if ((rc = reduce_add_norm(e, e->d_x, nw, B, sp->mm))) return rc;
     }
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107

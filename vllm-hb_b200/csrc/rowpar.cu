@@ -17,6 +17,9 @@
 //                      doing both hops (one-shot for small messages).
 //   HB_ROWPAR_NCCL     GEMM -> ncclAllReduce -> add + RMSNorm: the reference's sequence
 //                      (src/parallel/comm.rs:83-166), kept as the measured baseline.
+//   HB_ROWPAR_MULTIMEM the GEMM writes its partial into the world's multicast window; one
+//                      kernel reduces inside the NVLink switch, adds the residual and
+//                      normalises (ar_multimem.cu).
 #include "rowpar.h"
 
 #include <algorithm>
@@ -43,6 +46,12 @@ int rowpar_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_alg
   if (M < 1 || N < 1 || K_local < 1) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: bad shape");
   if (!w || w->ws == 1) return HB_ROWPAR_SINGLE;
   if (algo == HB_ALGO_NCCL) return HB_ROWPAR_NCCL;
+  if (algo == HB_ALGO_MULTIMEM) {
+    if (mm_ar_add_norm_supported(w, M, N, HB_BF16)) return HB_ROWPAR_MULTIMEM;
+    return fail(HB_ERR_INVALID_ARG,
+                "fused row-parallel: HB_ALGO_MULTIMEM needs a multicast window (hb_world_attach_multicast) that "
+                "holds %lld x %lld bf16, rows <= 256, N a multiple of 8 * ranks", (long long)M, (long long)N);
+  }
   if (!w->attached) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: world not attached to its peers yet");
   if (algo == HB_ALGO_AUTO || algo == HB_ALGO_TWO_SHOT) {
     // two hops pay from 128 KiB (and three ranks) on; below that one hop of everything
@@ -86,7 +95,10 @@ int rowpar_run(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, 
     return world_ar_add_norm(w, st, normed_out, resid_out, nullptr, resid_in, norm_w, M, N, eps, HB_BF16,
                              HB_ALGO_TWO_SHOT, &geo);
   }
+  if (form == HB_ROWPAR_MULTIMEM) partial = mm_partial_ptr(w);  // the GEMM writes into the window
   if ((rc = hb_gemm(st, partial, X, W, M, N, K_local, HB_BF16, gemm_ws))) return rc;
+  if (form == HB_ROWPAR_MULTIMEM)
+    return world_mm_ar_add_norm(w, st, normed_out, resid_out, partial, resid_in, norm_w, M, N, eps, HB_BF16);
   if (form == HB_ROWPAR_EXCHANGE)
     return world_ar_add_norm(w, st, normed_out, resid_out, partial, resid_in, norm_w, M, N, eps, HB_BF16,
                              algo == HB_ALGO_TWO_SHOT ? HB_ALGO_AUTO : algo);
