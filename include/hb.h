@@ -334,7 +334,8 @@ int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void
  *                       of the all-reduce is part of the GEMM kernel; one peer-memory kernel
  *                       then sums, adds the residual, returns the reduced slices and
  *                       normalises.  Taken with HB_ALGO_TWO_SHOT, or HB_ALGO_AUTO above
- *                       128 KiB on 3+ ranks, when N is a multiple of 128*ranks, M <= 256;
+ *                       (ranks-1) x M x N x 2 bytes >= 4 MiB on 3+ ranks, when N is a multiple of
+ *                       128*ranks, M <= 256;
  *   HB_ROWPAR_EXCHANGE  GEMM to a local partial, then hb_all_reduce_add_rms_norm
  *                       (HB_ALGO_ONE_SHOT, small messages, shapes the push form cannot take);
  *   HB_ROWPAR_NCCL      GEMM -> ncclAllReduce -> add + RMSNorm, the reference's own sequence

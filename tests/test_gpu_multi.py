@@ -163,7 +163,7 @@ def test_fused_rowparallel(hb, worlds, M, N, K_, algo):
     elif algo == "one_shot":
         assert form == "exchange"
     else:
-        assert form == ("push" if R > 2 and M * N * 2 > 128 * 1024 else "exchange")
+        assert form == ("push" if R > 2 and (R - 1) * M * N * 2 >= (4 << 20) else "exchange")
     for rep in range(3):
         outs = on_all(worlds, lambda r, w: hb.fused_rowparallel(w, *ins[r], 1e-5, code, workspace=wss[r]))
         assert all(w.status() == 0 for w in worlds)

@@ -359,7 +359,7 @@ int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resi
   const int R = w->ws;
   const size_t row_bytes = (size_t)N * dtype_size(dtype);
   bool two = algo == HB_ALGO_TWO_SHOT || staged;
-  if (algo == HB_ALGO_AUTO) two = staged || (R > 2 && (size_t)M * row_bytes > 128 * 1024);
+  if (algo == HB_ALGO_AUTO) two = staged || exchange_two_hops(R, (size_t)M * row_bytes);
   ArNormParams p;
   memset(&p, 0, sizeof(p));
   for (int q = 0; q < R; ++q) p.peer[q] = w->peer[q];

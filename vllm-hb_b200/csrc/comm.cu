@@ -234,7 +234,7 @@ int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_d
     return fail(HB_ERR_INVALID_ARG, "all_reduce: buffer must be 16-byte aligned and a multiple of 16 bytes");
   const int R = w->ws;
   bool two = algo == HB_ALGO_TWO_SHOT;
-  if (algo == HB_ALGO_AUTO) two = R > 2 && bytes > 128 * 1024;
+  if (algo == HB_ALGO_AUTO) two = exchange_two_hops(R, bytes);
   ArParams p;
   memset(&p, 0, sizeof(p));
   for (int q = 0; q < R; ++q) p.peer[q] = w->peer[q];

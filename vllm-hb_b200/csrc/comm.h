@@ -41,6 +41,17 @@ int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* r
 
 }  // namespace hb
 
+namespace hb {
+// Crossover of the exchange algorithms on peer memory.  One hop of everything ((R-1) x bytes
+// inbound per rank) against two hops of slices (2 (R-1)/R x bytes, a second flag wait): the
+// second hop pays once the inbound volume of the first form reaches about 4 MB (measured at
+// four ranks, rows of 16 KB: one-shot 24.7 us against 27.5 at 1 MB per rank, 31.9 against
+// 30.2 at 2 MB; at eight ranks two-shot was ahead from 1 MB per rank).  Two ranks: never.
+inline bool exchange_two_hops(int ranks, size_t bytes) {
+  return ranks > 2 && (size_t)(ranks - 1) * bytes >= ((size_t)4 << 20);
+}
+}  // namespace hb
+
 struct hb_world {
   int ws = 1, rank = 0, device = 0;
   cudaStream_t stream = nullptr;

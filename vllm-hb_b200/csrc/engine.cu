@@ -421,7 +421,7 @@ static int ensure_plans(hb_engine* e, int B, bool chunk, StepPlans** out) {
       sp.mm = e->ws > 1 && !mm_off && mm_ar_add_norm_supported(e->world, B, e->H, e->dtype);
       const char* pe = getenv("HB_PUSH");
       const bool off = pe && pe[0] == '0', always = pe && pe[0] == '1';
-      const bool two_hop = e->ws > 2 && (size_t)B * e->H * e->es > 128 * 1024;
+      const bool two_hop = exchange_two_hops(e->ws, (size_t)B * e->H * e->es);
       sp.push = e->ws > 1 && !sp.mm && !off && (always || two_hop) && push_exchange_supported(e->world, B, e->H, e->dtype);
       if (sp.push) {
         TcGemmPlan probe_o, probe_d;

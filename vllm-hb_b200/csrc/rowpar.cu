@@ -54,8 +54,8 @@ int rowpar_form(const hb_world* w, int64_t M, int64_t N, int64_t K_local, hb_alg
   }
   if (!w->attached) return fail(HB_ERR_INVALID_ARG, "fused row-parallel: world not attached to its peers yet");
   if (algo == HB_ALGO_AUTO || algo == HB_ALGO_TWO_SHOT) {
-    // two hops pay from 128 KiB (and three ranks) on; below that one hop of everything
-    const bool two_hop = algo == HB_ALGO_TWO_SHOT || (w->ws > 2 && (size_t)M * N * 2 > 128 * 1024);
+    // two hops pay once one hop of everything would bring 4 MiB into every rank (comm.h)
+    const bool two_hop = algo == HB_ALGO_TWO_SHOT || exchange_two_hops(w->ws, (size_t)M * N * 2);
     alignas(16) static char dummy[16];
     TcGemmPlan pl;
     if (two_hop && plan_push(&pl, w, dummy, dummy, M, N, K_local)) return HB_ROWPAR_PUSH;
