@@ -356,7 +356,8 @@ def tp_parity(hb, tp_world, rank: int, world: int, dev) -> dict:
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     digests = [None] * world
     dist.all_gather_object(digests, digest)
-    out.update({"ar_resid_bit_exact": bool(stats[0] == 0.0), "ar_norm_max_rel_err": float(stats[1]),
+    out.update({"engine_exchange": "switch reduction" if tp_world.has_multicast() else "peer memory",
+                "ar_resid_bit_exact": bool(stats[0] == 0.0), "ar_norm_max_rel_err": float(stats[1]),
                 "push_form": form, "push_max_rel_err": float(stats[2]), "push_ranks_identical": len(set(digests)) == 1,
                 "world_status_clean": bool(stats[3] == 0.0)})
     ok = (out.get("max_rel_err", 0.0) <= 2e-2 and out.get("ranks_identical", True) and out["ar_resid_bit_exact"]

@@ -132,6 +132,14 @@ def run_cases(hb, world, rank, ws, cuda, out):
     out["rowparallel"] = {"form": form, "max_rel_vs_nccl": d}
     if form != "multimem" or d > 2e-2:
         out["errors"].append(f"rank {rank}: fused row-parallel form {form}, off by {d:.4f}")
+    # a small tensor-parallel engine on this world (its row-parallel GEMMs write into the window
+    # and announce their completion themselves) against the oracle: the checks bench.py makes
+    import bench
+
+    par = bench.tp_parity(hb, world, rank, ws, cuda)
+    out["tp_parity"] = par
+    if rank == 0 and not par.get("ok", False):
+        out["errors"].append(f"tensor-parallel engine through the window: {par}")
     # time of the exchange alone, inside CUDA graphs: switch reduction against the peer-memory kernel
     N = 8192
     for M in (1, 8, 64, 128, 256):

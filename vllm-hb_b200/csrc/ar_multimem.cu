@@ -49,9 +49,15 @@ constexpr int kMmThreads = 256;   // as rms_norm_vec_kernel: same vector assignm
 constexpr int kMmMaxVec = 8;
 constexpr int kMmMaxRows = 256;
 
-struct MmCounters {       // window offset 0, written through the multicast address
+struct MmCounters {       // window offset 0
+  // written by every rank through the multicast address
   uint32_t ready[kMmMaxRows];
   uint32_t gathered[kMmMaxRows];
+  uint32_t ready_all;     // arrivals signalled by the producing GEMM itself (TcNormLink::ready_mc)
+  uint32_t pad[31];
+  // local only, never addressed through the multicast window
+  uint32_t gemm_calls;    // launches of a signalling GEMM on this rank so far
+  uint32_t gemm_ctas;     // CTAs of the running GEMM that are done
 };
 static_assert(sizeof(MmCounters) <= kFlagBytes, "multicast counters too large");
 
@@ -86,6 +92,7 @@ struct MmParams {
   int64_t slice_vecs;    // row_vecs / R
   float eps, n_feat;
   uint32_t spin;
+  int gemm_signals;      // the producing GEMM has announced this rank's partial (ready_all / gemm_calls)
 };
 
 template <int VPT>
@@ -133,10 +140,17 @@ mm_ar_add_norm_kernel(const MmParams p) {
   uint32_t target_c = 0;
   if (tid == 0) {
     const uint32_t mask = ~(uint32_t)(R - 1);
-    const uint32_t target_a = (peer_ld_acquire(&cnt->ready[row]) & mask) + (uint32_t)R;
     target_c = (peer_ld_acquire(&cnt->gathered[row]) & mask) + (uint32_t)R;
-    mm_red_add_release(&cnt_mc->ready[row], 1u);
-    ok = peer_wait_ge(&cnt->ready[row], target_a, p.spin);
+    if (p.gemm_signals) {
+      // the GEMM's last CTA has counted this call locally and told all ranks: every rank has
+      // made the same number of such calls, so R times this rank's count is the target
+      const uint32_t calls = *reinterpret_cast<volatile uint32_t*>(&cnt->gemm_calls);
+      ok = peer_wait_ge(&cnt->ready_all, calls * (uint32_t)R, p.spin);
+    } else {
+      const uint32_t target_a = (peer_ld_acquire(&cnt->ready[row]) & mask) + (uint32_t)R;
+      mm_red_add_release(&cnt_mc->ready[row], 1u);
+      ok = peer_wait_ge(&cnt->ready[row], target_a, p.spin);
+    }
   }
   bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
 
@@ -237,8 +251,16 @@ bool mm_ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype 
 
 void* mm_partial_ptr(const hb_world* w) { return w->mc_local ? (uint8_t*)w->mc_local + kFlagBytes : nullptr; }
 
+void mm_gemm_signal(const hb_world* w, uint32_t** ready_mc, uint32_t** calls, uint32_t** ctas) {
+  MmCounters* loc = reinterpret_cast<MmCounters*>(w->mc_local);
+  *ready_mc = &reinterpret_cast<MmCounters*>(w->mc_base)->ready_all;
+  *calls = &loc->gemm_calls;
+  *ctas = &loc->gemm_ctas;
+}
+
 int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
-                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype) {
+                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype,
+                         bool gemm_signals) {
   if (!mm_ar_add_norm_supported(w, M, N, dtype))
     return fail(HB_ERR_INVALID_ARG,
                 "all_reduce_add_rms_norm (multimem): needs an attached multicast window, bf16 rows of a multiple of "
@@ -250,6 +272,8 @@ int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* r
   if (normed_out && !norm_w) return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm: normed_out needs a weight");
   HB_CUDA_CHECK(cudaSetDevice(w->device));
   // a partial that is not already in the window is copied there (the engine's GEMMs write into it)
+  if (gemm_signals && partial != mm_partial_ptr(w))
+    return fail(HB_ERR_INVALID_ARG, "all_reduce_add_rms_norm (multimem): a GEMM that signals writes into the window");
   if (partial != mm_partial_ptr(w))
     HB_CUDA_CHECK(cudaMemcpyAsync(mm_partial_ptr(w), partial, (size_t)M * N * 2, cudaMemcpyDeviceToDevice, st));
   MmParams p;
@@ -268,6 +292,7 @@ int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* r
   p.eps = eps;
   p.n_feat = (float)N;
   p.spin = w->wait_limit;
+  p.gemm_signals = gemm_signals ? 1 : 0;
   const int64_t vpt = (p.row_vecs + kMmThreads - 1) / kMmThreads;
   if (vpt <= 1) mm_ar_add_norm_kernel<1><<<(unsigned)M, kMmThreads, 0, st>>>(p);
   else if (vpt <= 2) mm_ar_add_norm_kernel<2><<<(unsigned)M, kMmThreads, 0, st>>>(p);

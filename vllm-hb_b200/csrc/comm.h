@@ -36,8 +36,13 @@ static_assert(sizeof(CommFlags) <= kFlagBytes, "flag block too large");
 // nothing has to be copied.
 bool mm_ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
 void* mm_partial_ptr(const hb_world* w);
+// gemm_signals: the GEMM that wrote the partial (into the window) announced its completion to
+// all ranks itself (TcNormLink::ready_mc, counters from mm_gemm_signal): the kernel skips its
+// own arrival hop.
 int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
-                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype);
+                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype,
+                         bool gemm_signals = false);
+void mm_gemm_signal(const hb_world* w, uint32_t** ready_mc, uint32_t** calls, uint32_t** ctas);
 
 }  // namespace hb
 
@@ -92,13 +97,5 @@ bool push_exchange_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype d
 int world_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
                       const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps,
                       hb_dtype dtype, hb_algo algo, const PushGeometry* staged = nullptr);
-
-// The same operation with the sum done inside the NVLink switch (ar_multimem.cu); needs a
-// multicast window.  mm_partial_ptr: where inside the window a GEMM leaves its partial so that
-// nothing has to be copied.
-bool mm_ar_add_norm_supported(const hb_world* w, int64_t M, int64_t N, hb_dtype dtype);
-void* mm_partial_ptr(const hb_world* w);
-int world_mm_ar_add_norm(hb_world* w, cudaStream_t st, void* normed_out, void* resid_out, const void* partial,
-                         const void* resid_in, const void* norm_w, int64_t M, int64_t N, float eps, hb_dtype dtype);
 
 }  // namespace hb

@@ -516,7 +516,8 @@ static void prof_mark(hb_engine* e, int cat) {
 
 // h += SUM_ranks d_proj; x = norm(h; norm_w): one kernel over peer memory when the world has
 // several ranks (shapes the kernel does not take: all-reduce kernel, then add+norm), add+norm alone otherwise.
-static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B, bool mm = false) {
+static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B, bool mm = false,
+                           bool gemm_signals = false) {
   int rc;
   cudaStream_t st = e->stream;
   const float eps = (float)e->eps;
@@ -525,7 +526,7 @@ static int reduce_add_norm(hb_engine* e, void* x_out, const void* norm_w, int B,
     if (mm) {
       // the projection left its partial in the world's multicast window: the switch sums it
       if ((rc = world_mm_ar_add_norm(e->world, st, x_out, e->d_h, mm_partial_ptr(e->world), e->d_h, norm_w, B, e->H, eps,
-                                     e->dtype))) return rc;
+                                     e->dtype, gemm_signals))) return rc;
       ++e->last_launches;
       return HB_OK;
     }
@@ -583,6 +584,12 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
     push_link.push_rank = e->rank;
     push_link.push_spin = e->world->wait_limit;
   }
+  // exchange through the switch: the row-parallel GEMMs announce their completion themselves
+  // (HB_MM_SIGNAL=0: the exchange kernel does, with an arrival hop of its own)
+  static const bool mm_sig_off = [] { const char* v = getenv("HB_MM_SIGNAL"); return v && v[0] == '0'; }();
+  const bool mm_sig = sp->mm && e->use_tc && !mm_sig_off;
+  TcNormLink mm_link;
+  if (mm_sig) mm_gemm_signal(e->world, &mm_link.ready_mc, &mm_link.ready_calls, &mm_link.ready_ctas);
   if (rope_epi) {
     // the step's (cos, sin) table, shared by the q|k|v epilogues of every layer
     prof_mark(e, kCatRopeKv);
@@ -639,8 +646,8 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = run_gemm(e, sp, l, kO, e->d_x, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false, &produce))) return rc;
     } else {
       void* proj = sp->mm ? mm_partial_ptr(e->world) : e->d_proj;
-      if ((rc = run_gemm(e, sp, l, kO, proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false))) return rc;
-      if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B, sp->mm))) return rc;
+      if ((rc = run_gemm(e, sp, l, kO, proj, e->d_attn, w.wo, B, e->H, e->hq_l * e->hd, false, mm_sig ? &mm_link : nullptr))) return rc;
+      if ((rc = reduce_add_norm(e, e->d_x, w.norm_post, B, sp->mm, mm_sig))) return rc;
     }
     // mixture of experts: routing weights of every token       mixtral.rs:371-412
     if (e->moe) {
@@ -693,8 +700,8 @@ static int issue_step(hb_engine* e, StepPlans* sp, int B) {
       if ((rc = run_gemm(e, sp, l, kDown, e->d_x, e->d_act, w.wdown, B, e->H, e->I_e, false, &produce))) return rc;
     } else {
       void* proj = sp->mm ? mm_partial_ptr(e->world) : e->d_proj;
-      if ((rc = run_gemm(e, sp, l, kDown, proj, e->d_act, w.wdown, B, e->H, e->I_e, false))) return rc;
-      if ((rc = reduce_add_norm(e, e->d_x, nw, B, sp->mm))) return rc;
+      if ((rc = run_gemm(e, sp, l, kDown, proj, e->d_act, w.wdown, B, e->H, e->I_e, false, mm_sig ? &mm_link : nullptr))) return rc;
+      if ((rc = reduce_add_norm(e, e->d_x, nw, B, sp->mm, mm_sig))) return rc;
     }
   }
   // logits = x . lm_head^T (fp32 out), greedy argmax            llama_tp.rs:352-355, sampling/mod.rs:105-107

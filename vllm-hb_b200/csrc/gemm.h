@@ -66,6 +66,14 @@ struct TcNormLink {
   void* const* push_peers = nullptr;
   int push_ranks = 0, push_rank = 0;
   uint32_t push_spin = 0;
+  // independent of everything above: the GEMM announces its own completion to all ranks (the
+  // exchange through the NVLink switch, ar_multimem.cu, then starts without an arrival hop of
+  // its own).  The CTA that finishes last — counted in ready_ctas, which wraps back to zero —
+  // increments ready_calls (local, read by the exchange kernel as the number of calls so far)
+  // and adds 1 to the arrival counter of every rank through its multicast address.
+  uint32_t* ready_mc = nullptr;
+  uint32_t* ready_calls = nullptr;
+  uint32_t* ready_ctas = nullptr;
 };
 
 // A launch plan for one (M, N, K) problem: tensor maps are encoded once and passed by

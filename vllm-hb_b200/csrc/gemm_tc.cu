@@ -77,6 +77,9 @@ struct TcParams {
   int push_R, push_me, push_T;
   int64_t push_sv;
   uint32_t push_spin;
+  uint32_t* ready_mc;       // see TcNormLink::ready_mc
+  uint32_t* ready_calls;
+  uint32_t* ready_ctas;
   int recv_dedicated;       // cluster plans: the receive area of the exchange lies behind the pipeline buffers
   void* Y;
   float* partials;
@@ -755,6 +758,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
+  if (p.ready_mc && tid == 0) {
+    // this CTA's output is written (its bulk stores were issued by this thread, everybody
+    // else's plain stores precede the barrier above); the last CTA of the grid tells all ranks
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __threadfence();
+    const unsigned total = gridDim.x * gridDim.y;
+    if (atomicInc(p.ready_ctas, total - 1) == total - 1) {
+      __threadfence();
+      atomicAdd(p.ready_calls, 1u);
+      asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ready_mc), "r"(1u) : "memory");
+    }
+  }
   TC_TRACE(tid == 0, 7);
   TC_LAUNCH_TRACE(1);
   if (warp == 1) {
@@ -1108,6 +1123,13 @@ int gemm_tc_run(const TcGemmPlan& pl, cudaStream_t st, void* Y, int64_t ldy, voi
     p.rope_nq = link->n_q_heads;
     p.rope_nkv = link->n_kv_heads;
     p.kv_num_blocks = link->num_blocks;
+  }
+  if (link && link->ready_mc) {
+    if (!link->ready_calls || !link->ready_ctas)
+      return fail(HB_ERR_INVALID_ARG, "gemm_tc: the completion signal needs its two local counters");
+    p.ready_mc = link->ready_mc;
+    p.ready_calls = link->ready_calls;
+    p.ready_ctas = link->ready_ctas;
   }
   if (link && link->rowsq_in) {
     if (!p.tma_store || (pl.splits > 1 && !pl.cluster))
