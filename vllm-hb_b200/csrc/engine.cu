@@ -62,6 +62,7 @@ struct StepPlans {
   int q_group = 1;          // prefill chunks: consecutive positions that share an attention CTA
   bool defer_norm = false;  // add + norm folded into the GEMM epilogues (TcNormLink)
   bool mm = false;          // exchange through the NVLink switch (multicast window of the world)
+  const void* mm_window = nullptr;  // the window the plans (and the captured graph) were made for
   bool rope_epi = false;    // RoPE + KV write folded into the q|k|v GEMM epilogue (TcNormLink)
   bool push = false;        // o_proj / down_proj epilogues push their partials to the reducing ranks (kEpiPush)
   PushGeometry geo_o, geo_down;
@@ -383,8 +384,16 @@ static int pick_attn_splits(const hb_engine* e, int B) {
 static int ensure_plans(hb_engine* e, int B, bool chunk, StepPlans** out) {
   const int key = B | (chunk ? 1 << 20 : 0);
   auto it = e->plans.find(key);
-  if (it != e->plans.end()) { *out = &it->second; return HB_OK; }
+  const void* window = e->world ? e->world->mc_base : nullptr;
+  if (it != e->plans.end()) {
+    if (it->second.mm_window == window) { *out = &it->second; return HB_OK; }
+    // the world's multicast window was attached, detached or replaced since: the captured graph
+    // addresses the old one
+    if (it->second.graph) cudaGraphExecDestroy(it->second.graph);
+    e->plans.erase(it);
+  }
   StepPlans sp;
+  sp.mm_window = window;
   sp.attn_splits = pick_attn_splits(e, B);
   if (chunk && B > 1) {
     const int nrep = (int)(e->hq_l / e->hkv_l);
