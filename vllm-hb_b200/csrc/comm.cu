@@ -228,6 +228,9 @@ int world_all_reduce(hb_world* w, cudaStream_t st, void* buf, size_t count, hb_d
       return fail(HB_ERR_NCCL, "ncclAllReduce: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
     return HB_OK;
   }
+  if (algo == HB_ALGO_MULTIMEM)
+    return fail(HB_ERR_INVALID_ARG, "all_reduce: HB_ALGO_MULTIMEM exists for hb_all_reduce_add_rms_norm and hb_fused_rowparallel only");
+  if ((int)algo < 0 || (int)algo > HB_ALGO_MULTIMEM) return fail(HB_ERR_INVALID_ARG, "all_reduce: unknown algorithm %d", (int)algo);
   if (!w->attached) return fail(HB_ERR_INVALID_ARG, "all_reduce: world not attached to its peers yet");
   const size_t bytes = count * dtype_size(dtype);
   if (bytes % 16 || (reinterpret_cast<uintptr_t>(buf) & 15))
