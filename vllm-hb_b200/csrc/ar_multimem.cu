@@ -134,13 +134,15 @@ mm_ar_add_norm_kernel(const MmParams p) {
   pdl_launch_dependents();
   // A. this rank's partial is complete (the GEMM is an earlier kernel of the stream): tell
   // everybody, wait for everybody.  Both targets come from the counters as they stand before
-  // this rank's own arrival: `ready` may already hold up to R-1 arrivals of this call,
-  // `gathered` none (nobody passes A without this rank).
+  // this rank's own arrival: each may already hold up to R-1 arrivals of this call (peers can
+  // be ahead, by a whole phase when the GEMMs signal), never this rank's own, so rounding down
+  // to a multiple of R and adding R is exact.
   bool ok = true;
-  uint32_t target_c = 0;
+  __shared__ uint32_t s_target_c;
+  const uint32_t mask = ~(uint32_t)(R - 1);
+  // (a thread of another warp fetches the second counter meanwhile: two L2 round trips side by side)
+  if (tid == 32) s_target_c = (peer_ld_acquire(&cnt->gathered[row]) & mask) + (uint32_t)R;
   if (tid == 0) {
-    const uint32_t mask = ~(uint32_t)(R - 1);
-    target_c = (peer_ld_acquire(&cnt->gathered[row]) & mask) + (uint32_t)R;
     if (p.gemm_signals) {
       // the GEMM's last CTA has counted this call locally and told all ranks: every rank has
       // made the same number of such calls, so R times this rank's count is the target
@@ -186,7 +188,7 @@ mm_ar_add_norm_kernel(const MmParams p) {
   ok = true;
   if (all_ok && tid == 0) {
     mm_red_add_release(&cnt_mc->gathered[row], 1u);
-    ok = peer_wait_ge(&cnt->gathered[row], target_c, p.spin);
+    ok = peer_wait_ge(&cnt->gathered[row], s_target_c, p.spin);
   }
   all_ok = __syncthreads_and((all_ok && ok) ? 1 : 0) != 0;
 
