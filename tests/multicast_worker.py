@@ -140,6 +140,26 @@ def run_cases(hb, world, rank, ws, cuda, out):
     out["tp_parity"] = par
     if rank == 0 and not par.get("ok", False):
         out["errors"].append(f"tensor-parallel engine through the window: {par}")
+    # prefill in chunks (row counts 16, 16, 5: the exchange's calls differ in size) followed by
+    # decode steps, against the same tokens fed one by one: the two paths must agree
+    shape = dict(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=8,
+                 num_key_value_heads=8, vocab_size=2048, rms_norm_eps=1e-5, rope_theta=500000.0)
+    eng = hb.Engine.create_random(shape, seed=5, std=0.02, norm_ones=True, max_seq_len=64, bf16=True,
+                                  tensor_parallel_size=ws, world=world, max_batch=16)
+    ids = np.random.default_rng(3).integers(0, shape["vocab_size"], size=40).astype(np.uint32)
+    a, b = eng.create_kv_cache(), eng.create_kv_cache()
+    la = eng.forward_with_cache(ids[:37], 0, a)
+    for t in range(37):
+        lb = eng.forward_with_cache(ids[t:t + 1], t, b)
+    d0 = float(np.max(np.abs(la - lb))) / float(np.max(np.abs(lb)))
+    for t in range(37, 40):
+        la = eng.forward_with_cache(ids[t:t + 1], t, a)
+        lb = eng.forward_with_cache(ids[t:t + 1], t, b)
+    d1 = float(np.max(np.abs(la - lb))) / float(np.max(np.abs(lb)))
+    out["prefill_vs_stepwise"] = {"after_prefill": d0, "after_decode": d1}
+    if max(d0, d1) > 2e-2 or world.status() != 0:
+        out["errors"].append(f"rank {rank}: chunked prefill through the window differs from stepwise by {d0:.4f}/{d1:.4f}, status {world.status()}")
+    a.free(); b.free(); eng.close()
     # time of the exchange alone, inside CUDA graphs: switch reduction against the peer-memory kernel
     N = 8192
     for M in (1, 8, 64, 128, 256):

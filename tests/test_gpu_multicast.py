@@ -43,6 +43,7 @@ def test_switch_reduction_matches_oracle_and_peer_kernel(hb):
         pytest.skip("no switch reduction on this box: " + out["unavailable"])
     assert out["errors"] == []
     assert len(out["cases"]) == 6 and out["rowparallel"]["form"] == "multimem"
+    assert max(out["prefill_vs_stepwise"].values()) <= 2e-2   # calls of 16, 16 and 5 rows, then single rows
     assert out["tp_parity"]["ok"] and out["tp_parity"]["max_rel_err"] <= 2e-2 and out["tp_parity"]["ranks_identical"]
     for c in out["cases"]:
         assert c["max_rel_vs_oracle"] <= 2e-2 and c["max_rel_vs_peer_kernel"] <= 2e-2
