@@ -266,8 +266,8 @@ int hb_world_attach_ptrs(hb_world* w, void* const* peer_ptrs);
  * unbinding or freeing it, on every rank, and end no process while its window is bound.
  * After HB_ERR_TIMEOUT in a call that used the window its counters are out of step: detach
  * and attach again on all ranks.  bf16 rows only, world sizes 2, 4 and 8, hidden a multiple
- * of 8 * world_size, at most 256 rows.  hb_world_multicast_partial: the address inside the window where a
- * row-parallel GEMM should leave its [rows, hidden] partial; hb_all_reduce_add_rms_norm
+ * of 8 * world_size, at most 256 rows.  hb_world_multicast_partial: the address inside the
+ * window where a row-parallel GEMM should leave its [rows, hidden] partial; hb_all_reduce_add_rms_norm
  * copies a partial that lies elsewhere. */
 size_t hb_world_multicast_bytes(int64_t max_rows, int64_t hidden);
 int hb_world_attach_multicast(hb_world* w, void* local_ptr, void* multicast_ptr, size_t bytes);
@@ -316,7 +316,12 @@ int hb_all_reduce(hb_world* w, void* stream, void* buf, size_t count, hb_dtype d
  * values of hb_all_reduce followed by hb_add_rms_norm bit for bit.  partial, resid_in,
  * resid_out, normed_out are [rows, hidden] on this rank (resid_out may alias resid_in;
  * normed_out may be NULL); rows <= 256, hidden * element size a multiple of 16 bytes and
- * at most 32 KiB; every rank calls it with the same shapes. */
+ * at most 32 KiB; every rank calls it with the same shapes.
+ * HB_ALGO_MULTIMEM (world with a multicast window, bf16): the NVLink switch forms the sum —
+ * one load per 16 bytes returns the fp32-accumulated sum over all ranks, one store delivers
+ * the new residual slice to all ranks.  The switch adds in its own order, so the result
+ * agrees with the other algorithms to one bf16 rounding of the sum, not bit for bit; all
+ * ranks still hold identical rows.  A partial outside the window is copied into it first. */
 int hb_all_reduce_add_rms_norm(hb_world* w, void* stream, void* normed_out, void* resid_out,
                                const void* partial, const void* resid_in, const void* norm_w,
                                int64_t rows, int64_t hidden, float eps, hb_dtype dtype, hb_algo algo);
