@@ -946,6 +946,11 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
   } else {
     pl.splits = pick_cluster_splits(units, k_chunks, di.sm_count);
   }
+  // (Partner counts that are not powers of two, with shares of the batch rows that differ by
+  // four rows, were built and measured to cover more SMs where 28 tiles x 4 partners leave 36 of
+  // 148 idle: clusters of five do not pack into the GPCs - 28 of them are not resident together -
+  // and the 7168 x 8192 SwiGLU GEMM at M = 128 went from 32.4 to 59.9 us; three partners for the
+  // 8B q|k|v projection 18.1 against 16.5 us with four.  Removed again.)
   // a grid of at most one CTA per SM gains nothing from leaving room for a second one
   if (tuned && units * pl.splits <= di.sm_count) big = true;
   pl.stages = big ? big_stages : small_stages;
@@ -996,9 +1001,7 @@ int gemm_tc_plan(TcGemmPlan* plan, const void* X, const void* W, int64_t M, int6
     const size_t staged = cw * kTileN * out_elt + (epilogue == kEpiResidual ? 2 * cw * kTileN * 2 : 0);
     const size_t budget = (pl.stages == big_stages && big_stages > small_stages) ? big_budget : small_budget;
     const int st_d = budget > recv_bytes ? (int)std::min<size_t>(kMaxStages, (budget - recv_bytes) / stage) : 0;
-    static const int mode = [] { const char* v = getenv("HB_TC_RECV"); return v ? atoi(v) : -1; }();
-    const int min_stages = mode == 1 ? 2 : 3;
-    if (mode != 0 && st_d >= min_stages && staged <= (size_t)st_d * stage) {
+    if (st_d >= 3 && staged <= (size_t)st_d * stage) {
       pl.recv_dedicated = true;
       pl.stages = st_d;
     } else {
