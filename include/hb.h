@@ -45,7 +45,8 @@ typedef enum hb_dtype { HB_F32 = 0, HB_F16 = 1, HB_BF16 = 2 } hb_dtype;
 
 /* All-reduce algorithm selector. */
 typedef enum hb_algo {
-  HB_ALGO_AUTO = 0,     /* one-shot below the crossover size, two-shot above */
+  HB_ALGO_AUTO = 0,     /* peer memory: one-shot below the crossover size, two-shot above (never MULTIMEM,
+                           whose sums differ in the last bf16 digit: it is asked for by name) */
   HB_ALGO_ONE_SHOT = 1, /* every rank reads all partials: (R-1)*bytes inbound, one flag hop */
   HB_ALGO_TWO_SHOT = 2, /* reduce-scatter + all-gather: 2(R-1)/R*bytes, two flag hops */
   HB_ALGO_NCCL = 3,     /* ncclAllReduce: the reference's path, kept as the reported baseline */
